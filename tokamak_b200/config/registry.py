@@ -142,3 +142,6 @@ def _load_builtin() -> None:
     if "Logivik" not in _ARCHITECTURES:
         from ..models import logivik
         register_architecture(Architecture(logivik.ARCHITECTURE, logivik.parse_config, logivik.model_spec))
+    if "Tarivik" not in _ARCHITECTURES:
+        from ..models import tarivik
+        register_architecture(Architecture(tarivik.ARCHITECTURE, tarivik.parse_config, tarivik.model_spec))

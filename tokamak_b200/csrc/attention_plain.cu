@@ -15,7 +15,10 @@
 // a learned number whose exponential joins the softmax denominator once, with no key and no
 // value, neither scaled nor capped.  Queries may be float32 over bfloat16 pages and are addressed by
 // a token and a head stride; key and value rows have strides of their own, so that values which are the
-// leading elements of the key rows (a latent cache) are read from the key pages.
+// leading elements of the key rows (a latent cache) are read from the key pages.  Two more: a chunked
+// mask (chunk > 0: a query sees only the keys of its own block of `chunk` positions, blocks counted from
+// position 0 of the sequence) and a distance bias (slopes: one float per query head; the score of key j
+// for the query at position p loses slope * (p - j), after scale and cap).
 #include "common.cuh"
 
 namespace tk {
@@ -28,6 +31,7 @@ struct AttnParams {
   const void* k_cache;      // [num_pages, n_kv_heads, page_size, k_stride]: a row's first head_dim elements
   const void* v_cache;      // [num_pages, n_kv_heads, page_size, v_stride]: a row's first v_dim elements
   const float* sinks;       // [n_q_heads] or null
+  const float* slopes;      // [n_q_heads] or null
   const int* positions;     // [n_tokens]
   const int* tok_req;       // [n_tokens]
   const int* req_slot;      // [n_reqs]
@@ -35,7 +39,7 @@ struct AttnParams {
   const int* items;         // [n_items] token indices to process, or null for all tokens
   int* err;
   int n_tokens, n_reqs, n_q_heads, n_kv_heads, head_dim;
-  int page_size, max_pages, num_pages, window, v_dim;
+  int page_size, max_pages, num_pages, window, v_dim, chunk;
   long long q_tok_stride, q_head_stride;
   int k_stride, v_stride;
   float scale, softcap;
@@ -66,7 +70,9 @@ __global__ void attention_plain_kernel(AttnParams p) {
     return;
   }
   const int* table = p.block_table + (size_t)p.req_slot[r] * p.max_pages;
-  const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+  int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+  if (p.chunk > 0) lo = max(lo, pos - pos % p.chunk);
+  const float slope = p.slopes != nullptr ? p.slopes[hq] : 0.0f;
 
   const TQ* qrow = (const TQ*)p.q + (size_t)t * p.q_tok_stride + (size_t)hq * p.q_head_stride;
   float qreg[kPlainMaxPerLane];
@@ -100,6 +106,7 @@ __global__ void attention_plain_kernel(AttnParams p) {
     }
     dot = warp_sum(dot);
     if (p.softcap > 0.0f) dot = p.softcap * tanhf(dot * inv_cap);
+    dot -= slope * (float)(pos - j);
     const float m_new = fmaxf(m, dot);
     const float corr = expf(m - m_new);   // m = -inf on the first key: exp(-inf) = 0
     const float pj = expf(dot - m_new);
@@ -151,7 +158,8 @@ TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, con
                               int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                               int max_pages, int num_pages, int window, float scale, int dtype,
                               int v_dim, float softcap, const float* sinks, int q_dtype, long long q_tok_stride,
-                              long long q_head_stride, int k_stride, int v_stride, cudaStream_t stream) {
+                              long long q_head_stride, int k_stride, int v_stride, int chunk, const float* slopes,
+                              cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (v_dim <= 0) v_dim = head_dim;
   const int widest = head_dim > v_dim ? head_dim : v_dim;
@@ -165,7 +173,7 @@ TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, con
   p.items = items; p.err = err; p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads;
   p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
   p.max_pages = max_pages; p.num_pages = num_pages; p.window = window; p.scale = scale;
-  p.v_dim = v_dim; p.softcap = softcap; p.sinks = sinks;
+  p.v_dim = v_dim; p.softcap = softcap; p.sinks = sinks; p.chunk = chunk; p.slopes = slopes;
   p.q_tok_stride = q_tok_stride; p.q_head_stride = q_head_stride; p.k_stride = k_stride; p.v_stride = v_stride;
   dim3 grid(n_tokens, n_q_heads);
   cudaError_t e = cudaSuccess;

@@ -9,7 +9,12 @@
 // and the norm in front of the next sublayer.  Statistics, sums and the residual stream are
 // float32; `out` is rounded once to the activation type.  The branch comes in the activation
 // type or as float32 partial sums [parts, tokens, hidden] of a split-K product.
+//
+// Either norm may work in groups: the row is split into equal consecutive parts and each is divided by
+// its own root mean square (branch_norm_add_groups_kernel; one group is the plain norm).  That kernel also
+// takes a row without a branch: the norm in front alone.
 #include "common.cuh"
+#include "group_norm.cuh"
 
 namespace tk {
 
@@ -59,6 +64,58 @@ __global__ void branch_norm_add_kernel(float* __restrict__ resid, const T* __res
   ss2 = block_sum(ss2, scratch);
   const float rstd = rsqrtf(ss2 / (float)hidden + eps_n);
   for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = from_f32<T>(row[h] * rstd * next_w[h]);
+}
+
+// The general form with groups: the row lies in shared memory, a warp takes a group at a time.
+template <typename T>
+__global__ void branch_norm_add_groups_kernel(float* __restrict__ resid, const T* __restrict__ branch,
+                                              const float* __restrict__ parts, int n_parts, size_t part_stride,
+                                              const float* __restrict__ post_w, const float* __restrict__ layer_scale,
+                                              const float* __restrict__ next_w, T* __restrict__ out,
+                                              const int* __restrict__ rows, int hidden, float eps_b, float eps_n,
+                                              int groups_b, int groups_n) {
+  extern __shared__ float row[];          // the branch, then the new residual row; behind it the groups' statistics
+  float* rstd = row + hidden;
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* x = resid + (size_t)r * hidden;
+  const bool has_branch = branch != nullptr || parts != nullptr;
+  if (has_branch) {
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+      float b;
+      if (branch != nullptr) {
+        b = to_f32<T>(branch[(size_t)r * hidden + h]);
+      } else {
+        b = 0.0f;
+        for (int s = 0; s < n_parts; ++s) b += parts[(size_t)s * part_stride + (size_t)r * hidden + h];
+      }
+      row[h] = b;
+    }
+    group_rstd(row, hidden, groups_b, eps_b, rstd);
+  }
+  const int size_b = hidden / groups_b;
+  for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+    float v = x[h];
+    if (has_branch) {
+      float y = row[h] * rstd[h / size_b];
+      if (post_w != nullptr) y *= post_w[h];
+      if (layer_scale != nullptr) y *= layer_scale[h];
+      v += y;
+      if (rows == nullptr) x[h] = v;
+    }
+    row[h] = v;
+  }
+  if (out == nullptr) return;
+  T* o = out + (size_t)i * hidden;
+  if (next_w == nullptr) {
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = from_f32<T>(row[h]);
+    return;
+  }
+  group_rstd(row, hidden, groups_n, eps_n, rstd);
+  const int size_n = hidden / groups_n;
+  for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = from_f32<T>(row[h] * rstd[h / size_n] * next_w[h]);
 }
 
 // Four neighbouring elements at once (the address is a multiple of four elements).
@@ -164,12 +221,36 @@ __global__ void __launch_bounds__(512) branch_norm_add_vec_kernel(float* __restr
 TK_API int tk_branch_norm_add(float* resid, const void* branch, const float* parts, int n_parts,
                               long long part_stride, const float* post_w, const float* layer_scale,
                               const float* next_w, void* out, const int* rows, int n_rows, int hidden,
-                              float eps_b, float eps_n, int dtype, cudaStream_t stream) {
+                              float eps_b, float eps_n, int groups_b, int groups_n, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  if (hidden < 1 || hidden > 12288 || (branch == nullptr) == (parts == nullptr)) {
+  const bool grouped = groups_b > 1 || groups_n > 1 || (branch == nullptr && parts == nullptr);
+  if (hidden < 1 || hidden > 12288 || (branch != nullptr && parts != nullptr) || groups_b < 1 || groups_n < 1 ||
+      hidden % groups_b || hidden % groups_n) {
     return (int)cudaErrorInvalidValue;
   }
   cudaError_t e = cudaSuccess;
+  if (grouped) {
+    const int threads = hidden >= 1024 ? 256 : 128;
+    const int most = groups_b > groups_n ? groups_b : groups_n;
+    const size_t smem = (size_t)(hidden + most) * sizeof(float);
+    if (smem > 96 * 1024) return (int)cudaErrorInvalidValue;
+#define TK_BRANCH_NORM_GROUPS(T)                                                                                       \
+    do {                                                                                                               \
+      if (smem > 48 * 1024) {                                                                                          \
+        e = cudaFuncSetAttribute(tk::branch_norm_add_groups_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                 (int)smem);                                                                           \
+        if (e != cudaSuccess) return (int)e;                                                                           \
+      }                                                                                                                \
+      e = tk::launch(tk::branch_norm_add_groups_kernel<T>, dim3((unsigned)n_rows), dim3(threads), smem, stream, resid, \
+                     (const T*)branch, parts, n_parts, (size_t)part_stride, post_w, layer_scale, next_w, (T*)out,      \
+                     rows, hidden, eps_b, eps_n, groups_b, groups_n);                                                  \
+    } while (0)
+    if (dtype == tk::kF32) { TK_BRANCH_NORM_GROUPS(float); }
+    else if (dtype == tk::kBF16) { TK_BRANCH_NORM_GROUPS(__nv_bfloat16); }
+    else return (int)cudaErrorInvalidValue;
+#undef TK_BRANCH_NORM_GROUPS
+    return (int)e;
+  }
   if (hidden % 4 == 0) {
     const int quads = hidden / 4;
     const int threads = quads >= 512 ? 512 : (quads + 31) / 32 * 32;

@@ -12,7 +12,8 @@ namespace tk {
 // resid[t, :] = float(table[ids[t], :]) * scale                 (src/tokamak/model/transformer.py:140)
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ resid, int hidden, int vocab, float scale, int* err) {
+                                    float* __restrict__ resid, int hidden, int vocab, float scale, int accumulate,
+                                    int* err) {
   pdl_trigger();
   if (threadIdx.x == 0) tl_mark(4, 0);
   pdl_wait();
@@ -22,10 +23,16 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
   float* out = resid + (size_t)t * hidden;
   if (id < 0 || id >= vocab) {
     if (threadIdx.x == 0) set_error(err, kErrTokenId, t, id, vocab);
-    for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[h] = 0.0f;
+    if (!accumulate) {
+      for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[h] = 0.0f;
+    }
     return;
   }
   const T* row = table + (size_t)id * hidden;
+  if (accumulate) {     // a second table's rows join the rows that are there (a learned position table)
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[h] += to_f32<T>(row[h]) * scale;
+    return;
+  }
   for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[h] = to_f32<T>(row[h]) * scale;
 }
 
@@ -230,13 +237,13 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, const float* __restr
 TK_TIMELINE_SETTER(elementwise)
 
 TK_API int tk_embed_gather(const void* table, int dtype, const int* ids, float* resid, int n_tokens,
-                           int hidden, int vocab, float scale, int* err, cudaStream_t stream) {
+                           int hidden, int vocab, float scale, int accumulate, int* err, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,
                     e = tk::launch(tk::embed_gather_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream,
-                                       (const T*)table, ids, resid, hidden, vocab, scale, err));
+                                       (const T*)table, ids, resid, hidden, vocab, scale, accumulate, err));
   return (int)e;
 }
 

@@ -16,7 +16,7 @@ _P = c_void_p
 
 # name -> argument types (every function returns a cudaError_t as int unless noted)
 _SIGNATURES: dict[str, list] = {
-    "tk_embed_gather": [_P, c_int, _P, _P, c_int, c_int, c_int, c_float, _P, _P],
+    "tk_embed_gather": [_P, c_int, _P, _P, c_int, c_int, c_int, c_float, c_int, _P, _P],
     "tk_step_begin": [_P, c_int, c_int, _P, c_int, _P, c_longlong, _P, _P, _P, _P, _P, c_int, c_int, _P, _P],
     "tk_decode_begin": [_P, c_int, c_int, _P, c_int, _P, c_longlong, _P, c_int, c_int, _P, _P, _P, _P, _P],
     "tk_sample_slots": [_P, c_longlong, _P, _P, c_int, _P, c_int, c_int, _P, _P],
@@ -35,7 +35,8 @@ _SIGNATURES: dict[str, list] = {
     "tk_rope_table": [_P, _P, _P, c_int, c_int, c_float, _P],
     "tk_attention_plain": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                           c_float, c_int, c_int, c_float, _P, c_int, c_longlong, c_longlong, c_int, c_int, _P],
+                           c_float, c_int, c_int, c_float, _P, c_int, c_longlong, c_longlong, c_int, c_int, c_int, _P,
+                           _P],
     "tk_latent_prepare": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                           _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
@@ -52,7 +53,27 @@ _SIGNATURES: dict[str, list] = {
     "tk_gemm_f32_batched": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong,
                             c_longlong, _P],
     "tk_branch_norm_add": [_P, _P, _P, c_int, c_longlong, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_float,
-                           c_int, _P],
+                           c_int, c_int, c_int, _P],
+    "tk_short_conv": [_P, _P, c_int, c_longlong, _P, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "tk_hgrn2_prepare": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
+                         c_int, _P],
+    "tk_mlstm_prepare": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_float, c_float,
+                         _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "tk_mlstm_out": [_P, _P, _P, _P, c_int, c_longlong, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float,
+                     c_float, c_int, _P],
+    "tk_ssd_prepare": [_P, _P, _P, c_int, c_longlong, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                       c_int, _P],
+    "tk_ssd_out": [_P, _P, c_int, _P, _P, c_int, c_longlong, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
+                   c_int, c_float, c_float, c_int, _P],
+    "tk_gate_scale": [_P, _P, _P, c_int, c_longlong, c_int, c_int, _P, c_int, c_int, c_int, c_float, c_int, _P],
+    "tk_qkv_rownorm": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P,
+                       _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                       c_float, c_int, _P],
+    "tk_moe_tile_rows": [],
+    "tk_moe_route": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "tk_moe_ffn": [_P, c_longlong, c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "tk_moe_combine": [_P, _P, _P, c_int, c_int, c_int, _P],
     "tk_qkv_pairs": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                      c_float, c_int, _P],

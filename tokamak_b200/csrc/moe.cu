@@ -1,0 +1,276 @@
+// A mixture of gated feed-forward experts with a sigmoid router.
+//
+//   s = sigmoid(W_r h)                       scores, float32
+//   c = s + correction                       choice scores
+//   the experts form equal groups of neighbours; a group's score is the sum of its two largest c; only
+//   experts of the `keep` best groups can be chosen; the `top` experts with the largest c are chosen
+//   out = sum over the chosen e of s_e * W_down,e (act(W_gate,e h) * (W_up,e h))
+//
+// Five kernels.  moe_route_kernel: a warp per token forms the logits and makes the choice (ties go to the
+// lower index).  moe_sort_kernel: one block counts the (token, choice) pairs of every expert, lays the
+// pairs out expert by expert and lists the row tiles of the products.  moe_ffn_kernel: the experts'
+// products over those tiles, first gate and up with the activation, then down; an output element is
+// one thread's sum over ascending k, so a pair's result does not depend on what else is in the batch or
+// where its row lies in a tile.  moe_combine_kernel: the weighted sum of a token's pairs in the order of
+// its choices, float32.
+#include "common.cuh"
+
+namespace tk {
+
+constexpr int kMoeMaxExperts = 1024;
+constexpr int kMoeTileRows = 32;
+constexpr int kMoeTileCols = 64;
+constexpr int kMoeTileK = 32;
+
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+// h: [n_tokens, width] activation type; router: [experts, width] float32; one warp per token.
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router,
+                                 const float* __restrict__ correction, int* __restrict__ chosen,
+                                 float* __restrict__ weights, int n_tokens, int width, int experts, int n_groups,
+                                 int keep, int top) {
+  extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= n_tokens) return;
+  float* s = smem + (size_t)warp * (2 * experts + n_groups);
+  float* c = s + experts;
+  float* gs = c + experts;
+  const T* x = h + (size_t)t * width;
+  for (int e = 0; e < experts; ++e) {
+    const float* w = router + (size_t)e * width;
+    float acc = 0.0f;
+    for (int i = lane; i < width; i += 32) acc += to_f32<T>(x[i]) * w[i];
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      s[e] = 1.0f / (1.0f + expf(-acc));
+      c[e] = s[e] + (correction != nullptr ? correction[e] : 0.0f);
+    }
+  }
+  __syncwarp();
+  const int size = experts / n_groups;
+  if (keep < n_groups) {
+    for (int g = lane; g < n_groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;          // the two largest
+      for (int i = 0; i < size; ++i) {
+        const float v = c[g * size + i];
+        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+      }
+      gs[g] = size >= 2 ? a + b : a;
+    }
+    __syncwarp();
+    for (int it = 0; it < keep; ++it) {
+      float best = -INFINITY; int bi = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && (v > best || (v == best && g < bi))) { best = v; bi = g; }
+      }
+      warp_argmax(best, bi);
+      if (lane == 0 && bi < n_groups) gs[bi] = INFINITY;      // taken
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32) {
+      if (gs[e / size] != INFINITY) c[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  for (int it = 0; it < top; ++it) {
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = c[e];
+      if (v > best || (v == best && e < bi && v != -INFINITY)) { best = v; bi = e; }
+    }
+    warp_argmax(best, bi);
+    if (bi >= experts) bi = 0;        // fewer experts allowed than asked for: refused by the host
+    if (lane == 0) {
+      chosen[(size_t)t * top + it] = bi;
+      weights[(size_t)t * top + it] = s[bi];
+      c[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+// order: [pairs] the pairs (token * top + choice) expert by expert; tiles: [max_tiles, 3] (expert, first
+// place in order, rows) of every tile of kMoeTileRows rows; n_tiles: [1].
+__global__ void moe_sort_kernel(const int* __restrict__ chosen, int* __restrict__ order, int* __restrict__ tiles,
+                                int* __restrict__ n_tiles, int pairs, int experts) {
+  __shared__ int count[kMoeMaxExperts], start[kMoeMaxExperts], cursor[kMoeMaxExperts], tile0[kMoeMaxExperts];
+  pdl_trigger();
+  pdl_wait();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = chosen[i];
+    if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tile = 0;
+    for (int e = 0; e < experts; ++e) {
+      start[e] = at; tile0[e] = tile;
+      at += count[e];
+      tile += (count[e] + kMoeTileRows - 1) / kMoeTileRows;
+    }
+    *n_tiles = tile;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = chosen[i];
+    if (e >= 0 && e < experts) order[start[e] + atomicAdd(&cursor[e], 1)] = i;
+  }
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int n = (count[e] + kMoeTileRows - 1) / kMoeTileRows;
+    for (int i = 0; i < n; ++i) {
+      int* tile = tiles + (size_t)(tile0[e] + i) * 3;
+      tile[0] = e; tile[1] = start[e] + i * kMoeTileRows; tile[2] = min(kMoeTileRows, count[e] - i * kMoeTileRows);
+    }
+  }
+}
+
+struct MoeFfnParams {
+  const void* a;            // rows of the left operand, activation type
+  long long a_stride;
+  int a_div;                // row of pair i is i / a_div (top for the tokens' rows, 1 for rows per pair)
+  const void* b0;           // [experts, n_out, k] activation type
+  const void* b1;           // the same for the second product of a gated unit, or null
+  void* out;                // row of pair i: gated [pairs, n_out] activation type, else float32
+  const int* order; const int* tiles; const int* n_tiles;
+  int n_out, k, act;
+};
+
+template <typename T, bool kGated>
+__global__ void __launch_bounds__(256) moe_ffn_kernel(MoeFfnParams p) {
+  __shared__ float As[kMoeTileRows][kMoeTileK + 1];
+  __shared__ float Bs[kGated ? 2 : 1][kMoeTileCols][kMoeTileK + 1];
+  __shared__ int rows[kMoeTileRows];
+  pdl_trigger();
+  pdl_wait();
+  if ((int)blockIdx.x >= *p.n_tiles) return;
+  const int* tile = p.tiles + (size_t)blockIdx.x * 3;
+  const int e = tile[0], first = tile[1], n_rows = tile[2];
+  const int n0 = blockIdx.y * kMoeTileCols;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  if (tid < kMoeTileRows) rows[tid] = tid < n_rows ? p.order[first + tid] : -1;
+  __syncthreads();
+  const T* b0 = (const T*)p.b0 + (size_t)e * p.n_out * p.k;
+  const T* b1 = kGated ? (const T*)p.b1 + (size_t)e * p.n_out * p.k : nullptr;
+  float acc[2][4] = {}, acc1[2][4] = {};
+  const int lk = tid & 31, lr = tid >> 5;
+  for (int k0 = 0; k0 < p.k; k0 += kMoeTileK) {
+    const bool kin = k0 + lk < p.k;
+#pragma unroll
+    for (int i = 0; i < kMoeTileRows / 8; ++i) {
+      const int r = lr + 8 * i, pair = rows[r];
+      As[r][lk] = (pair >= 0 && kin) ? to_f32<T>(((const T*)p.a)[(size_t)(pair / p.a_div) * p.a_stride + k0 + lk]) : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < kMoeTileCols / 8; ++i) {
+      const int c = lr + 8 * i;
+      const bool in = kin && n0 + c < p.n_out;
+      Bs[0][c][lk] = in ? to_f32<T>(b0[(size_t)(n0 + c) * p.k + k0 + lk]) : 0.0f;
+      if (kGated) Bs[1][c][lk] = in ? to_f32<T>(b1[(size_t)(n0 + c) * p.k + k0 + lk]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kMoeTileK; ++kk) {
+      const float a0 = As[2 * ty][kk], a1 = As[2 * ty + 1][kk];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float b = Bs[0][tx + 16 * i][kk];
+        acc[0][i] += a0 * b; acc[1][i] += a1 * b;
+        if (kGated) {
+          const float u = Bs[1][tx + 16 * i][kk];
+          acc1[0][i] += a0 * u; acc1[1][i] += a1 * u;
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int pair = rows[2 * ty + j];
+    if (pair < 0) continue;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = n0 + tx + 16 * i;
+      if (c >= p.n_out) continue;
+      if (kGated) ((T*)p.out)[(size_t)pair * p.n_out + c] = from_f32<T>(glu_act(acc[j][i], p.act) * acc1[j][i]);
+      else ((float*)p.out)[(size_t)pair * p.n_out + c] = acc[j][i];
+    }
+  }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, float* __restrict__ out,
+                                   int n_tokens, int width, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n_tokens * width) return;
+  const int t = (int)(idx / width), c = (int)(idx - (long long)t * width);
+  float acc = 0.0f;
+  for (int k = 0; k < top; ++k) acc += weights[(size_t)t * top + k] * y[((size_t)t * top + k) * width + c];
+  out[idx] = acc;
+}
+
+}  // namespace tk
+
+TK_API int tk_moe_tile_rows() { return tk::kMoeTileRows; }
+
+TK_API int tk_moe_route(const void* h, const float* router, const float* correction, int* chosen, float* weights,
+                        int* order, int* tiles, int* n_tiles, int n_tokens, int width, int experts, int n_groups,
+                        int keep, int top, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (experts < 1 || experts > tk::kMoeMaxExperts || n_groups < 1 || experts % n_groups || keep < 1 || keep > n_groups ||
+      top < 1 || top > keep * (experts / n_groups)) {
+    return (int)cudaErrorInvalidValue;
+  }
+  const int warps = 4;
+  const size_t smem = (size_t)warps * (2 * experts + n_groups) * sizeof(float);
+  cudaError_t e = cudaSuccess;
+  TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::moe_route_kernel<T>, dim3((unsigned)((n_tokens + warps - 1) / warps)),
+                                             dim3(warps * 32), smem, stream, (const T*)h, router, correction, chosen,
+                                             weights, n_tokens, width, experts, n_groups, keep, top));
+  if (e != cudaSuccess) return (int)e;
+  e = tk::launch(tk::moe_sort_kernel, dim3(1), dim3(1024), 0, stream, (const int*)chosen, order, tiles, n_tiles,
+                 n_tokens * top, experts);
+  return (int)e;
+}
+
+// gated != 0: out[pair] = act(a[pair / a_div] b0^T) * (a[pair / a_div] b1^T) in the activation type;
+// else out[pair] = a[pair / a_div] b0^T in float32.
+TK_API int tk_moe_ffn(const void* a, long long a_stride, int a_div, const void* b0, const void* b1, void* out,
+                      const int* order, const int* tiles, const int* n_tiles, int max_tiles, int n_out, int k, int act,
+                      int dtype, cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  if (n_out < 1 || k < 1 || a_div < 1) return (int)cudaErrorInvalidValue;
+  tk::MoeFfnParams p;
+  p.a = a; p.a_stride = a_stride; p.a_div = a_div; p.b0 = b0; p.b1 = b1; p.out = out;
+  p.order = order; p.tiles = tiles; p.n_tiles = n_tiles; p.n_out = n_out; p.k = k; p.act = act;
+  const dim3 grid((unsigned)max_tiles, (unsigned)((n_out + tk::kMoeTileCols - 1) / tk::kMoeTileCols));
+  cudaError_t e = cudaSuccess;
+  if (b1 != nullptr) {
+    TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::moe_ffn_kernel<T, true>, grid, dim3(256), 0, stream, p));
+  } else {
+    TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::moe_ffn_kernel<T, false>, grid, dim3(256), 0, stream, p));
+  }
+  return (int)e;
+}
+
+TK_API int tk_moe_combine(const float* y, const float* weights, float* out, int n_tokens, int width, int top,
+                          cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  const long long total = (long long)n_tokens * width;
+  return (int)tk::launch(tk::moe_combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, y, weights,
+                         out, n_tokens, width, top);
+}

@@ -73,15 +73,17 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, err: torch.Tensor,
-                 scale: float = 1.0) -> None:
-    """resid[t] = float32(table[ids[t]]) * scale."""
+                 scale: float = 1.0, accumulate: bool = False) -> None:
+    """resid[t] = float32(table[ids[t]]) * scale; with ``accumulate`` the rows are added to what
+    ``resid`` holds (a second table, looked up by position)."""
     _want(table, None, "table"); _want(ids, torch.int32, "ids"); _want(resid, torch.float32, "resid")
     n = ids.numel()
     vocab, hidden = table.shape
     if resid.shape[-1] != hidden or resid.numel() < n * hidden:
         raise KernelError("resid is too small for the tokens")
     _check(_lib().tk_embed_gather(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(),
-                                     resid.data_ptr(), n, hidden, vocab, float(scale), err.data_ptr(), _stream()),
+                                     resid.data_ptr(), n, hidden, vocab, float(scale), int(accumulate), err.data_ptr(),
+                                     _stream()),
            "embed_gather")
 
 
@@ -342,7 +344,8 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
                     positions: torch.Tensor, tok_req: torch.Tensor, req_slot: torch.Tensor,
                     block_table: torch.Tensor, err: torch.Tensor, *, scale: float,
                     window: int | None = None, items: torch.Tensor | None = None,
-                    softcap: float | None = None, sinks: torch.Tensor | None = None) -> None:
+                    softcap: float | None = None, sinks: torch.Tensor | None = None,
+                    chunk: int | None = None, slopes: torch.Tensor | None = None) -> None:
     """Paged attention of a mixed batch; q is [N, Hq, d], out [N, Hq, dv] with dv the size of a
     value head (``v_cache`` is ``[pages, Hkv, page, dv]``).
 
@@ -351,8 +354,14 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     elements of the key rows (a cache whose values are part of its keys).  ``items`` restricts the
     work to the listed token indices (rows of q and out).  ``softcap`` bounds the scaled scores
     (``cap * tanh(score / cap)``); ``sinks`` is one float32 per query head whose exponential joins
-    the softmax denominator."""
+    the softmax denominator.  ``chunk``: a query sees only the keys of its own block of ``chunk``
+    positions (blocks counted from position 0).  ``slopes`` (float32, one per query head): the score of
+    the key at distance ``n`` behind the query loses ``slope * n``."""
     _want(out, k_cache.dtype, "out"); _want(k_cache, None, "k_cache")
+    if slopes is not None:
+        _want(slopes, torch.float32, "slopes")
+        if slopes.numel() != q.shape[1]:
+            raise KernelError("one slope per query head is needed")
     if not q.is_cuda or q.dtype not in (k_cache.dtype, torch.float32) or q.stride(2) != 1:
         raise KernelError("q must be a CUDA tensor in the pages' type or float32 with a dense last axis")
     n, hq, d = q.shape
@@ -380,7 +389,7 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
                                         block_table.shape[1], num_pages, int(window or 0),
                                         float(scale), dtype_code(k_cache.dtype), dv, float(softcap or 0.0),
                                         _ptr(sinks), dtype_code(q.dtype), q.stride(0), q.stride(1), d, v_stride,
-                                        _stream()),
+                                        int(chunk or 0), _ptr(slopes), _stream()),
            "attention_plain")
 
 
@@ -453,19 +462,30 @@ def _parts_of(x: torch.Tensor, like: torch.dtype, name: str):
     return x, None, 0, x.shape[0], x.shape[1]
 
 
-def branch_norm_add(resid: torch.Tensor, branch: torch.Tensor, post_weight: torch.Tensor | None,
+def branch_norm_add(resid: torch.Tensor, branch: torch.Tensor | None, post_weight: torch.Tensor | None,
                     layer_scale: torch.Tensor | None, branch_eps: float, next_weight: torch.Tensor | None,
-                    out: torch.Tensor | None, next_eps: float = 0.0, rows: torch.Tensor | None = None) -> None:
+                    out: torch.Tensor | None, next_eps: float = 0.0, rows: torch.Tensor | None = None,
+                    branch_groups: int = 1, next_groups: int = 1) -> None:
     """``x = resid + rmsnorm(branch) * post_weight * layer_scale`` (written back unless ``rows``
     selects rows), then, if ``out`` is given, ``out = rmsnorm(x) * next_weight`` or, without
     ``next_weight``, ``out = x`` in the activation type.  ``branch`` is in the activation type or
-    float32 partial sums ``[parts, tokens, hidden]``."""
+    float32 partial sums ``[parts, tokens, hidden]``; ``None``: nothing joins, only the norm in front
+    runs.  ``branch_groups`` / ``next_groups``: the norm works on that many equal consecutive parts of
+    a row, each with a root mean square of its own."""
     _want(resid, torch.float32, "resid")
     hidden = resid.shape[-1]
-    dtype = out.dtype if out is not None else (branch.dtype if branch.dim() == 2 else torch.float32)
-    b, parts, n_parts, n, width = _parts_of(branch, dtype, "branch")
-    if width != hidden or n != resid.shape[0]:
-        raise KernelError("branch and resid differ in shape")
+    if hidden % branch_groups or hidden % next_groups:
+        raise KernelError(f"a row of {hidden} does not split into {branch_groups} / {next_groups} equal groups")
+    if branch is None:
+        if out is None:
+            return
+        dtype, b, parts, n_parts = out.dtype, None, None, 0
+    else:
+        dtype = out.dtype if out is not None else (branch.dtype if branch.dim() == 2 else torch.float32)
+        b, parts, n_parts, n, width = _parts_of(branch, dtype, "branch")
+        if width != hidden or n != resid.shape[0]:
+            raise KernelError("branch and resid differ in shape")
+    n = resid.shape[0]
     for name, t in (("post_weight", post_weight), ("layer_scale", layer_scale), ("next_weight", next_weight)):
         if t is not None:
             _want(t, torch.float32, name)
@@ -481,7 +501,8 @@ def branch_norm_add(resid: torch.Tensor, branch: torch.Tensor, post_weight: torc
     _check(_lib().tk_branch_norm_add(resid.data_ptr(), _ptr(b), _ptr(parts), n_parts,
                                         parts.stride(0) if parts is not None else 0, _ptr(post_weight),
                                         _ptr(layer_scale), _ptr(next_weight), _ptr(out), _ptr(rows), n_rows, hidden,
-                                        float(branch_eps), float(next_eps), dtype_code(dtype), _stream()),
+                                        float(branch_eps), float(next_eps), int(branch_groups), int(next_groups),
+                                        dtype_code(dtype), _stream()),
            "branch_norm_add")
 
 
@@ -619,6 +640,257 @@ def gla_out(o: torch.Tensor, proj: torch.Tensor | None, g_off: int, weight: torc
     _check(_lib().tk_gla_out(o.data_ptr(), _ptr(x), _ptr(parts), n_parts, row, g_off, _ptr(weight), y.data_ptr(),
                                 n, heads, dv, float(eps), dtype_code(dtype), _stream()), "gla_out")
     return y
+
+
+
+def _stacked_args(proj: torch.Tensor, like: torch.dtype, name: str) -> tuple:
+    """``(x pointer, parts pointer, parts, stride of a part, row length, tokens)`` of a product's result."""
+    x, parts, n_parts, n, row = _parts_of(proj, like, name)
+    return _ptr(x), _ptr(parts), n_parts, parts.stride(0) if parts is not None else 0, row, n
+
+
+def short_conv(rows: torch.Tensor, taps: torch.Tensor, tail: torch.Tensor | None, step, *, dtype: torch.dtype,
+               in_off: int = 0, channels: int | None = None, bias: torch.Tensor | None = None,
+               add_input: bool = False, silu: bool = False, out_f32: bool = False) -> torch.Tensor:
+    """A causal convolution of ``taps.shape[1]`` taps per channel over every request's tokens of the step,
+    continued from the request's *tail*: ``tail[slot]`` is float32 ``[taps - 1, channels]``, the inputs of
+    the positions before the step (zeros before the sequence), and is moved on to the step's last inputs.
+
+    ``rows`` is the float32 residual stream ``[tokens, width]``, a product's result in ``dtype`` or its
+    float32 partial sums; the channels are the columns from ``in_off`` on.  ``y = [x +] [bias +] conv(x)``,
+    then silu if asked; float32 sums; the result is ``[tokens, channels]`` in ``dtype`` (or float32)."""
+    _want(taps, torch.float32, "taps")
+    ch, k = taps.shape
+    channels = ch if channels is None else channels
+    if channels != ch:
+        raise KernelError("one row of taps per channel is needed")
+    rows_f32 = None
+    if rows.dim() == 2 and rows.dtype == torch.float32 and dtype != torch.float32:
+        _want(rows, torch.float32, "rows")
+        rows_f32, x, parts, n_parts, part_stride, row, n = rows.data_ptr(), None, None, 0, 0, rows.shape[1], rows.shape[0]
+    else:
+        x, parts, n_parts, part_stride, row, n = _stacked_args(rows, dtype, "rows")
+    if bias is not None:
+        _want(bias, torch.float32, "bias")
+    if k > 1:
+        _want(tail, torch.float32, "tail")
+        if tail.shape[1:] != (k - 1, channels):
+            raise KernelError("the tail must be [slots, taps - 1, channels]")
+    out = torch.empty((n, channels), dtype=torch.float32 if out_f32 else dtype, device=taps.device)
+    move = 1 if step.max_q_len == 1 else 2
+    _check(_lib().tk_short_conv(x, parts, n_parts, part_stride, rows_f32, row, in_off, taps.data_ptr(), _ptr(bias),
+                                   _ptr(tail), out.data_ptr(), step.tok_req.data_ptr(), step.req_q_start.data_ptr(),
+                                   step.req_q_len.data_ptr(), step.req_slot.data_ptr(), step.err.data_ptr(), n,
+                                   step.req_slot.numel(), tail.shape[0] if tail is not None else 0, channels, k,
+                                   int(add_input), int(silu), int(out_f32), move, dtype_code(dtype), _stream()),
+           "short_conv")
+    return out
+
+
+def _prep_buffer(n: int, heads: int, dk: int, dv: int, device) -> torch.Tensor:
+    dks, dvs = gla_prepared_row(dk, dv)
+    return torch.empty(n * heads * (3 * dks + dvs), dtype=torch.float32, device=device)
+
+
+def hgrn2_prepare(proj: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor, *, dtype: torch.dtype, q_off: int,
+                  f_off: int, v_off: int, heads: int, key_dim: int, value_dim: int) -> torch.Tensor:
+    """The inputs of :func:`gla_scan` for linear attention whose forget gate is also its key:
+    ``q = silu(z_q)``, ``f = lower + (1 - lower) sigmoid(z_f + f_bias)``, ``alpha = f``, ``k = 1 - f``, ``v = z_v``."""
+    _want(f_bias, torch.float32, "f_bias"); _want(lower, torch.float32, "lower")
+    x, parts, n_parts, part_stride, row, n = _stacked_args(proj, dtype, "proj")
+    prep = _prep_buffer(n, heads, key_dim, value_dim, f_bias.device)
+    _check(_lib().tk_hgrn2_prepare(x, parts, n_parts, part_stride, row, q_off, f_off, v_off, f_bias.data_ptr(),
+                                      lower.data_ptr(), prep.data_ptr(), n, heads, key_dim, value_dim,
+                                      dtype_code(dtype), _stream()), "hgrn2_prepare")
+    return prep
+
+
+def mlstm_prepare(proj: torch.Tensor, i_bias: torch.Tensor, f_bias: torch.Tensor, m_state: torch.Tensor, step, *,
+                  dtype: torch.dtype, q_off: int, k_off: int, v_off: int, i_off: int, f_off: int, heads: int,
+                  key_dim: int, value_dim: int, cap: float, q_scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(prep, gates)``: the inputs of :func:`gla_scan` for a matrix memory with exponential gates whose
+    normaliser rides as one more value column (the state is ``[heads, key_dim, value_dim + 1]``), and
+    ``gates`` float32 ``[tokens, heads, 3]`` = ``(alpha, exp(i - m), exp(-m))``.  ``m_state`` ``[slots, heads]``
+    holds every request's running maximum and is moved on."""
+    for name, t in (("i_bias", i_bias), ("f_bias", f_bias), ("m_state", m_state)):
+        _want(t, torch.float32, name)
+    x, parts, n_parts, part_stride, row, n = _stacked_args(proj, dtype, "proj")
+    prep = _prep_buffer(n, heads, key_dim, value_dim + 1, m_state.device)
+    gates = torch.empty((n, heads, 3), dtype=torch.float32, device=m_state.device)
+    _check(_lib().tk_mlstm_prepare(x, parts, n_parts, part_stride, row, q_off, k_off, v_off, i_off, f_off,
+                                      i_bias.data_ptr(), f_bias.data_ptr(), float(cap), float(q_scale),
+                                      m_state.data_ptr(), gates.data_ptr(), prep.data_ptr(),
+                                      step.req_q_start.data_ptr(), step.req_q_len.data_ptr(), step.req_slot.data_ptr(),
+                                      step.err.data_ptr(), n, step.req_slot.numel(), m_state.shape[0], heads, key_dim,
+                                      value_dim, dtype_code(dtype), _stream()), "mlstm_prepare")
+    return prep, gates
+
+
+def mlstm_out(o: torch.Tensor, gates: torch.Tensor, proj: torch.Tensor, g_off: int, weight: torch.Tensor, eps: float,
+              dtype: torch.dtype, out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor:
+    """``o`` is ``[tokens, heads, dv + 1]`` with ``n . q`` in the last column: every head's
+    ``o / (max(|n . q|, exp(-m)) + 1e-6)`` is scaled to unit root mean square, multiplied by ``weight``
+    (one per channel of all heads) and by ``sigmoid(gate)``, the gate read from ``proj`` at ``g_off``."""
+    _want(o, torch.float32, "o"); _want(gates, torch.float32, "gates"); _want(weight, torch.float32, "weight")
+    n, heads, dv1 = o.shape
+    dv = dv1 - 1
+    x, parts, n_parts, part_stride, row, n2 = _stacked_args(proj, dtype, "proj")
+    if n2 != n or weight.numel() != heads * dv or g_off < 0 or g_off + heads * dv > row:
+        raise KernelError("mlstm_out shape mismatch")
+    if out is None:
+        out = torch.empty((n, heads * dv), dtype=dtype, device=o.device)
+    _check(_lib().tk_mlstm_out(o.data_ptr(), gates.data_ptr(), x, parts, n_parts, part_stride, row, g_off,
+                                  weight.data_ptr(), out.data_ptr(), out.stride(0), n, heads, dv, float(eps),
+                                  float(out_scale), dtype_code(dtype), _stream()), "mlstm_out")
+    return out
+
+
+def ssd_prepare(xbc: torch.Tensor, proj: torch.Tensor, dt_off: int, dt_bias: torch.Tensor, a_log: torch.Tensor, *,
+                dtype: torch.dtype, heads: int, groups: int, state: int, value_dim: int) -> torch.Tensor:
+    """The inputs of :func:`gla_scan` for a state-space layer with a scalar decay per head.  ``xbc`` is
+    float32 ``[tokens, heads * value_dim + 2 * groups * state]`` (x | B | C after their convolution);
+    ``dt = softplus(proj[:, dt_off + h] + dt_bias)``, ``alpha = exp(-exp(a_log) dt)``, ``k = B``, ``q = C`` of the
+    head's group, ``v = dt x``."""
+    for name, t in (("xbc", xbc), ("dt_bias", dt_bias), ("a_log", a_log)):
+        _want(t, torch.float32, name)
+    x, parts, n_parts, part_stride, row, n = _stacked_args(proj, dtype, "proj")
+    if xbc.shape != (n, heads * value_dim + 2 * groups * state):
+        raise KernelError("ssd_prepare shape mismatch")
+    prep = _prep_buffer(n, heads, state, value_dim, xbc.device)
+    _check(_lib().tk_ssd_prepare(xbc.data_ptr(), x, parts, n_parts, part_stride, row, dt_off, dt_bias.data_ptr(),
+                                    a_log.data_ptr(), prep.data_ptr(), n, heads, groups, state, value_dim,
+                                    dtype_code(dtype), _stream()), "ssd_prepare")
+    return prep
+
+
+def ssd_out(o: torch.Tensor, xbc: torch.Tensor, proj: torch.Tensor, z_off: int, skip: torch.Tensor,
+            weight: torch.Tensor, norm_groups: int, eps: float, dtype: torch.dtype, out: torch.Tensor | None = None,
+            out_scale: float = 1.0) -> torch.Tensor:
+    """``norm((o + skip_h x) * silu(z)) * weight`` with the RMS norm over ``norm_groups`` equal parts of the
+    row; ``x`` are the leading columns of ``xbc``, ``z`` the columns of ``proj`` from ``z_off`` on."""
+    for name, t in (("o", o), ("xbc", xbc), ("skip", skip), ("weight", weight)):
+        _want(t, torch.float32, name)
+    n, heads, dv = o.shape
+    x, parts, n_parts, part_stride, row, n2 = _stacked_args(proj, dtype, "proj")
+    if n2 != n or weight.numel() != heads * dv or skip.numel() != heads or (heads * dv) % norm_groups:
+        raise KernelError("ssd_out shape mismatch")
+    if out is None:
+        out = torch.empty((n, heads * dv), dtype=dtype, device=o.device)
+    _check(_lib().tk_ssd_out(o.data_ptr(), xbc.data_ptr(), xbc.stride(0), x, parts, n_parts, part_stride, row, z_off,
+                                skip.data_ptr(), weight.data_ptr(), out.data_ptr(), out.stride(0), n, heads, dv,
+                                int(norm_groups), float(eps), float(out_scale), dtype_code(dtype), _stream()), "ssd_out")
+    return out
+
+
+def gate_scale(x: torch.Tensor, proj: torch.Tensor, g_off: int, out: torch.Tensor | None = None,
+               scale: float = 1.0) -> torch.Tensor:
+    """``x * sigmoid(gate) * scale`` with the gate read from ``proj`` at column ``g_off``; ``out`` may be a
+    column range of wider rows."""
+    _want(x, None, "x")
+    n, cols = x.shape
+    g, parts, n_parts, part_stride, row, n2 = _stacked_args(proj, x.dtype, "proj")
+    if n2 != n or g_off < 0 or g_off + cols > row:
+        raise KernelError("the gate columns lie outside the row")
+    if out is None:
+        out = torch.empty_like(x)
+    _check(_lib().tk_gate_scale(x.data_ptr(), g, parts, n_parts, part_stride, row, g_off, out.data_ptr(),
+                                   out.stride(0), n, cols, float(scale), dtype_code(x.dtype), _stream()), "gate_scale")
+    return out
+
+
+def qkv_rownorm(proj: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step,
+                block_table: torch.Tensor, *, q_off: int, k_off: int, v_off: int, q_bias, k_bias, v_bias, q_norm,
+                k_norm, eps: float) -> None:
+    """Biases, an RMS norm over a token's whole query projection and over its whole key projection (one
+    weight per channel; ``None``: no norm), queries to ``q_out`` ``[tokens, Hq, d]``, keys and values into
+    their pages."""
+    n, hq, d = q_out.shape
+    num_pages, hkv, page_size, dk = k_cache.shape
+    dv = v_cache.shape[3]
+    if dk != d or not q_out.is_contiguous():
+        raise KernelError("qkv_rownorm shape mismatch")
+    for name, t, size in (("q_bias", q_bias, hq * d), ("k_bias", k_bias, hkv * d), ("v_bias", v_bias, hkv * dv),
+                          ("q_norm", q_norm, hq * d), ("k_norm", k_norm, hkv * d)):
+        if t is not None:
+            _want(t, torch.float32, name)
+            if t.numel() != size:
+                raise KernelError(f"{name} does not match the projection")
+    x, parts, n_parts, part_stride, row, n2 = _stacked_args(proj, q_out.dtype, "proj")
+    if n2 != n:
+        raise KernelError("proj and q_out differ in tokens")
+    _check(_lib().tk_qkv_rownorm(x, parts, n_parts, part_stride, row, q_off, k_off, v_off, _ptr(q_bias), _ptr(k_bias),
+                                    _ptr(v_bias), _ptr(q_norm), _ptr(k_norm), q_out.data_ptr(), k_cache.data_ptr(),
+                                    v_cache.data_ptr(), step.positions.data_ptr(), step.tok_req.data_ptr(),
+                                    step.req_slot.data_ptr(), block_table.data_ptr(), step.req_q_len.data_ptr(),
+                                    step.req_kv_len.data_ptr(), step.err.data_ptr(), n, step.req_slot.numel(), hq, hkv,
+                                    d, dv, page_size, block_table.shape[1], num_pages, float(eps),
+                                    dtype_code(q_out.dtype), _stream()), "qkv_rownorm")
+
+
+def moe_tile_rows() -> int:
+    return _lib().tk_moe_tile_rows()
+
+
+class MoeRouting:
+    """What :func:`moe_route` leaves on the device: ``chosen`` / ``weights`` ``[tokens, top]``, the pairs
+    ``token * top + choice`` laid out expert by expert (``order``), and the products' row tiles."""
+
+    def __init__(self, chosen, weights, order, tiles, n_tiles, max_tiles):
+        self.chosen, self.weights, self.order, self.tiles, self.n_tiles, self.max_tiles = (
+            chosen, weights, order, tiles, n_tiles, max_tiles)
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, *, top: int, n_groups: int,
+              keep: int) -> MoeRouting:
+    """Scores ``sigmoid(h router^T)`` in float32, choice by score plus ``correction`` among the ``keep`` groups
+    of neighbouring experts whose two best choice scores add up highest, weights the plain scores."""
+    _want(h, None, "h"); _want(router, torch.float32, "router")
+    n, width = h.shape
+    experts = router.shape[0]
+    if correction is not None:
+        _want(correction, torch.float32, "correction")
+    if router.shape[1] != width or experts % n_groups or not 1 <= keep <= n_groups or not 1 <= top <= keep * (experts // n_groups):
+        raise KernelError("moe_route: sizes do not fit")
+    dev = h.device
+    pairs = n * top
+    max_tiles = min(pairs, -(-pairs // moe_tile_rows()) + experts)
+    chosen = torch.empty((n, top), dtype=torch.int32, device=dev)
+    weights = torch.empty((n, top), dtype=torch.float32, device=dev)
+    order = torch.empty(pairs, dtype=torch.int32, device=dev)
+    tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=dev)
+    n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    _check(_lib().tk_moe_route(h.data_ptr(), router.data_ptr(), _ptr(correction), chosen.data_ptr(), weights.data_ptr(),
+                                  order.data_ptr(), tiles.data_ptr(), n_tiles.data_ptr(), n, width, experts, n_groups,
+                                  keep, top, dtype_code(h.dtype), _stream()), "moe_route")
+    return MoeRouting(chosen, weights, order, tiles, n_tiles, max_tiles)
+
+
+def moe_experts(h: torch.Tensor, routing: MoeRouting, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                activation: str = "silu") -> torch.Tensor:
+    """The weighted sum of the chosen experts' gated units, float32 ``[tokens, width]``.  ``w_gate`` and
+    ``w_up`` are ``[experts, ff, width]``, ``w_down`` ``[experts, width, ff]``, all in the type of ``h``."""
+    n, width = h.shape
+    experts, ff, _ = w_gate.shape
+    top = routing.chosen.shape[1]
+    for name, t, shape in (("w_gate", w_gate, (experts, ff, width)), ("w_up", w_up, (experts, ff, width)),
+                           ("w_down", w_down, (experts, width, ff))):
+        _want(t, h.dtype, name)
+        if t.shape != shape:
+            raise KernelError(f"{name} must be {shape}")
+    pairs = n * top
+    act = torch.empty((pairs, ff), dtype=h.dtype, device=h.device)
+    y = torch.empty((pairs, width), dtype=torch.float32, device=h.device)
+    out = torch.empty((n, width), dtype=torch.float32, device=h.device)
+    lib, r = _lib(), routing
+    _check(lib.tk_moe_ffn(h.data_ptr(), h.stride(0), top, w_gate.data_ptr(), w_up.data_ptr(), act.data_ptr(),
+                          r.order.data_ptr(), r.tiles.data_ptr(), r.n_tiles.data_ptr(), r.max_tiles, ff, width,
+                          GLU_ACTIVATIONS[activation], dtype_code(h.dtype), _stream()), "moe_ffn (gate, up)")
+    _check(lib.tk_moe_ffn(act.data_ptr(), ff, 1, w_down.data_ptr(), None, y.data_ptr(), r.order.data_ptr(),
+                          r.tiles.data_ptr(), r.n_tiles.data_ptr(), r.max_tiles, width, ff, 0, dtype_code(h.dtype),
+                          _stream()), "moe_ffn (down)")
+    _check(lib.tk_moe_combine(y.data_ptr(), r.weights.data_ptr(), out.data_ptr(), n, width, top, _stream()),
+           "moe_combine")
+    return out
 
 
 def decode_splits(n_items: int, n_kv_heads: int, max_kv_len: int) -> int:

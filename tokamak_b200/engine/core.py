@@ -177,6 +177,6 @@ def random_core(raw_config: dict, *, seed: int = 0, std: float = 0.02, norm_std:
     expected = DecoderModel.expected_tensors(spec)
     tensors = random_tensors(expected, seed, std, norm_std, dt, device=dev)
     for name, req in expected.items():
-        if req.role in ("vector", "bias", "fraction") and name in tensors:
+        if req.role in ("vector", "bias", "fraction", "matrix_f32") and name in tensors:
             tensors[name] = tensors[name].float()
     return EngineCore("<random>", dtype=dt, device=dev, tensors=tensors, raw_config=raw_config, **kwargs)

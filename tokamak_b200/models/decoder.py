@@ -48,6 +48,22 @@ class ModelSpec:
                 raise ValueError(f"the schedule names an unknown block {call.block!r}")
 
 
+def flat_needs(key, need) -> list[tuple]:
+    """``(cache key, need)`` pairs of a block's need.  A block that keeps several things per request (pages
+    for one mixer, state records for another, records of its own) declares a dictionary ``{name: need}``,
+    nested at will; its entries become the cache keys ``key/name``."""
+    if isinstance(need, dict):
+        return [pair for name, sub in need.items() for pair in flat_needs(f"{key}/{name}", sub)]
+    return [] if need is None else [(key, need)]
+
+
+def views_of(cache, key, need):
+    """The view, or the dictionary of views in the shape of the block's need."""
+    if isinstance(need, dict):
+        return {name: views_of(cache, f"{key}/{name}", sub) for name, sub in need.items()}
+    return None if need is None else cache.view(key)
+
+
 class DecoderModel:
     """Embedding, the scheduled blocks, final norm and head
     (src/tokamak/model/transformer.py:112-176), built from a :class:`ModelSpec`."""
@@ -67,6 +83,7 @@ class DecoderModel:
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, spec.final_norm_name,
                                                           tensors, rt)
         self.head = HEADS.get(spec.head.kind)(spec.head, self.embedding, tensors, rt)
+        self._needs = {name: block.cache_need() for name, block in self.blocks.items()}
 
     @staticmethod
     def expected_tensors(spec: ModelSpec) -> dict[str, TensorReq]:
@@ -109,9 +126,10 @@ class DecoderModel:
                 continue
             if call.cache is None:
                 raise ValueError(f"block {call.block!r} needs a cache and the schedule names none")
-            if call.cache in needs and needs[call.cache] != need:
-                raise ValueError(f"cache {call.cache!r} is shared by blocks with different needs")
-            needs.setdefault(call.cache, need)
+            for key, sub in flat_needs(call.cache, need):
+                if key in needs and needs[key] != sub:
+                    raise ValueError(f"cache {key!r} is shared by blocks with different needs")
+                needs.setdefault(key, sub)
         return needs
 
     def forward(self, step) -> torch.Tensor:
@@ -122,7 +140,7 @@ class DecoderModel:
         pending = None
         schedule = self.spec.schedule
         for i, call in enumerate(schedule):
-            view = step.cache.view(call.cache) if call.cache is not None else None
+            view = views_of(step.cache, call.cache, self._needs[call.block]) if call.cache is not None else None
             block = self.blocks[call.block]
             if getattr(block, "TAKES_NEXT_NORM", False):
                 # the norm that will consume what the block leaves pending: the next block's, or the last

@@ -256,6 +256,143 @@ class CappedAttention:
         return linear(out.view(n, spec.num_heads * spec.v_head_dim), self.w_o, err=step.err)
 
 
+@dataclass(frozen=True)
+class RowNormAttentionSpec:
+    """Sizes and constants of an attention mixer with the options of :class:`RowNormAttention`.
+
+    ``bias``: q, k and v projections have biases.  ``row_norm_eps`` switches the RMS norm over the *whole*
+    query projection of a token (all heads at once, a weight per channel) and over the whole key projection
+    on.  ``chunk``: a query sees only the keys of its own block of that many positions.  ``slope_exponent``:
+    the score of a key ``n`` positions behind the query loses ``slope_h * n`` with
+    ``slope_h = 2 ** (-slope_exponent * (h + 1) / heads)`` (``None``: no distance bias).  ``sinks``: a learned
+    number per query head joins the softmax denominator.  ``gate``: the concatenated heads are multiplied by
+    ``sigmoid(W_g h)``.  The ``*_name`` fields are the tensors' names after the part's prefix.
+    """
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    softmax_scale: float
+    bias: bool = True
+    row_norm_eps: float | None = None
+    chunk: int | None = None
+    window: int | None = None
+    slope_exponent: float | None = None
+    sinks: bool = False
+    gate: bool = False
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    o_name: str = "o"
+    gate_name: str = "g"
+    bias_suffix: str = ".b"
+    norm_suffix: str = ".norm"
+    sink_name: str = "sink"
+    kind: str = "attention_rownorm"
+
+
+@MIXERS.register("attention_rownorm")
+class RowNormAttention:
+    """Grouped-query attention over paged keys and values without rotation: positions enter through a
+    distance bias on the scores and through a chunked mask.  Query head ``h`` reads key/value head
+    ``h // (Hq / Hkv)``; ``score = (q . k) * scale - slope_h * (i - j)``; position ``i`` sees ``j <= i`` of its own
+    chunk (chunks are counted from position 0 of the sequence, wherever a prompt was cut); the softmax
+    denominator also holds ``exp(sink_h)``.
+
+    The q, k, v and gate matrices are one stacked operand.  Biases, row norms and the page write are one
+    kernel (``csrc/qkv_rownorm.cu``); scores, bias, softmax and the weighted sum run in float32 inside the
+    attention kernel; the gate and the caller's factor are one kernel.  :meth:`branch` writes the rows in
+    front of the output projection into a buffer of the caller's (see :class:`~tokamak_b200.parts.parallel.ParallelMixer`).
+    """
+
+    GRAPH_SAFE = True
+
+    def __init__(self, spec: RowNormAttentionSpec, prefix: str, tensors: dict[str, torch.Tensor], rt: Runtime):
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"{spec.num_heads} query heads are not a multiple of "
+                             f"{spec.num_kv_heads} key/value heads")
+        if max(spec.head_dim, spec.v_head_dim) > 1024:
+            raise ValueError(f"head sizes {spec.head_dim} / {spec.v_head_dim} are beyond the attention kernel's 1024")
+        if spec.chunk is not None and spec.chunk < 1:
+            raise ValueError(f"a chunk of {spec.chunk} positions is none")
+        self.spec = spec
+        self.rt = rt
+        t = lambda name: tensors[prefix + name]
+        mats = [t(spec.q_name), t(spec.k_name), t(spec.v_name)] + ([t(spec.gate_name)] if spec.gate else [])
+        self.w_in = torch.cat(mats, dim=0).contiguous()
+        nq, nk = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        self.q_off, self.k_off, self.v_off = 0, nq, nq + nk
+        self.g_off = nq + nk + spec.num_kv_heads * spec.v_head_dim
+        vec = lambda name: t(name).contiguous()
+        self.q_bias = vec(spec.q_name + spec.bias_suffix) if spec.bias else None
+        self.k_bias = vec(spec.k_name + spec.bias_suffix) if spec.bias else None
+        self.v_bias = vec(spec.v_name + spec.bias_suffix) if spec.bias else None
+        self.q_norm = vec(spec.q_name + spec.norm_suffix) if spec.row_norm_eps is not None else None
+        self.k_norm = vec(spec.k_name + spec.norm_suffix) if spec.row_norm_eps is not None else None
+        self.sinks = vec(spec.sink_name) if spec.sinks else None
+        self.slopes = None
+        if spec.slope_exponent is not None:
+            heads = torch.arange(1, spec.num_heads + 1, dtype=torch.float64)
+            self.slopes = torch.pow(2.0, -spec.slope_exponent * heads / spec.num_heads).to(torch.float32).to(rt.device)
+        self.w_o = t(spec.o_name)
+        self.out_width = spec.num_heads * spec.v_head_dim
+        self.prefill_heads = spec.num_heads
+
+    @staticmethod
+    def expected_tensors(spec: RowNormAttentionSpec, prefix: str) -> dict[str, TensorReq]:
+        h, d, dv = spec.hidden_size, spec.head_dim, spec.v_head_dim
+        nq, nk, nv = spec.num_heads * d, spec.num_kv_heads * d, spec.num_kv_heads * dv
+        out = {}
+        for name, rows in ((spec.q_name, nq), (spec.k_name, nk), (spec.v_name, nv)):
+            out[prefix + name] = TensorReq((rows, h))
+            if spec.bias:
+                out[prefix + name + spec.bias_suffix] = TensorReq((rows,), role="bias")
+        if spec.row_norm_eps is not None:
+            out[prefix + spec.q_name + spec.norm_suffix] = TensorReq((nq,), role="vector")
+            out[prefix + spec.k_name + spec.norm_suffix] = TensorReq((nk,), role="vector")
+        if spec.sinks:
+            out[prefix + spec.sink_name] = TensorReq((spec.num_heads,), role="bias")
+        if spec.gate:
+            out[prefix + spec.gate_name] = TensorReq((spec.num_heads * dv, h))
+        out[prefix + spec.o_name] = TensorReq((h, spec.num_heads * dv))
+        return out
+
+    def cache_need(self) -> KVPagesNeed:
+        s = self.spec
+        return KVPagesNeed(s.num_kv_heads, s.head_dim, s.window, None if s.v_head_dim == s.head_dim else s.v_head_dim)
+
+    def weight_bytes(self) -> int:
+        return tensor_bytes(self.w_in, self.w_o, self.q_bias, self.k_bias, self.v_bias, self.q_norm, self.k_norm,
+                            self.sinks)
+
+    def branch(self, h, step, cache_view, out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor:
+        spec = self.spec
+        n = h.shape[0]
+        proj = linear(h, self.w_in, err=step.err)
+        q = torch.empty((n, spec.num_heads, spec.head_dim), dtype=h.dtype, device=h.device)
+        ops.qkv_rownorm(proj, q, cache_view.k, cache_view.v, step, cache_view.table, q_off=self.q_off,
+                        k_off=self.k_off, v_off=self.v_off, q_bias=self.q_bias, k_bias=self.k_bias,
+                        v_bias=self.v_bias, q_norm=self.q_norm, k_norm=self.k_norm, eps=spec.row_norm_eps or 0.0)
+        att = torch.empty((n, spec.num_heads, spec.v_head_dim), dtype=h.dtype, device=h.device)
+        paged_attention(q, att, cache_view, step, scale=spec.softmax_scale, window=spec.window, sinks=self.sinks,
+                        chunk=spec.chunk, slopes=self.slopes)
+        att = att.view(n, self.out_width)
+        if not spec.gate:
+            if out is None and out_scale == 1.0:
+                return att
+            res = att.float().mul_(out_scale).to(h.dtype)
+            if out is None:
+                return res
+            out.copy_(res)
+            return out
+        return ops.gate_scale(att, proj, self.g_off, out=out, scale=out_scale)
+
+    def forward(self, h, step, cache_view):
+        return linear(self.branch(h, step, cache_view), self.w_o, err=step.err)
+
+
 _SIDE: dict = {}
 
 
@@ -269,12 +406,15 @@ def _side_stream(device: torch.device):
 
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, scale: float,
-                    window: int | None, softcap: float | None = None, sinks: torch.Tensor | None = None) -> None:
+                    window: int | None, softcap: float | None = None, sinks: torch.Tensor | None = None,
+                    chunk: int | None = None, slopes: torch.Tensor | None = None) -> None:
     """Attention of every token of the step over the pages of its own request.
 
     ``softcap`` bounds the scaled scores by ``cap * tanh(score / cap)``; ``sinks`` (float32, one per
     query head) adds ``exp(sink)`` to every softmax denominator.  ``out`` is ``[N, Hq, dv]`` where
-    the value heads have a size of their own.
+    the value heads have a size of their own.  ``chunk`` (a query sees only its own block of that many
+    positions) and ``slopes`` (a distance bias per query head) are known to the general kernel, which
+    then runs every token of the step.
 
     Chooses the kernels.  A latent cache in bfloat16 goes to the tensor-core kernel that stacks the heads
     of a token (``csrc/attention_latent.cu``).  bfloat16 with a head_dim the tiled kernels take: single next
@@ -283,6 +423,11 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     and every other shape, runs on the general kernel.
     """
     ops.flush_chains()     # q and the pages may come from a product that is still queued: launch it on this stream
+    if chunk is not None or slopes is not None:
+        ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req, step.req_slot,
+                            cache_view.table, step.err, scale=scale, window=window, softcap=softcap, sinks=sinks,
+                            chunk=chunk, slopes=slopes)
+        return
     n, hq, d = q.shape
     hkv, page = cache_view.k.shape[1], cache_view.k.shape[2]
     bf16 = q.dtype == torch.bfloat16

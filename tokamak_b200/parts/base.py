@@ -95,7 +95,9 @@ class TensorReq:
     dtype; ``vector`` (norm weights and other small per-channel tensors) is held in
     float32, which keeps a tensor stored in 32-bit exact; ``int_table`` becomes int32.
     ``bias`` and ``fraction`` are held like ``vector`` and differ only in what seeded random
-    weights put there: values around 0, or inside (0, 1), instead of around 1.
+    weights put there: values around 0, or inside (0, 1), instead of around 1.  ``matrix_f32`` is a
+    matrix (drawn like one) that is held in float32 in every engine dtype: a router, whose product is
+    a 32-bit one.
     """
 
     shape: tuple[int, ...]
@@ -186,13 +188,15 @@ class NormedBranch:
     norm that consumes it (:meth:`RMSNorm.add_norm <tokamak_b200.parts.norm.RMSNorm.add_norm>`)
     does the output norm, the layer scale, the residual sum and its own normalisation in one
     kernel.  ``x`` is what :func:`linear` returned (activation type, or float32 partial sums);
-    ``weight`` and ``layer_scale`` are float32 vectors or ``None``.
+    ``weight`` and ``layer_scale`` are float32 vectors or ``None``.  ``groups``: the norm works on
+    that many equal consecutive parts of a row, each divided by its own root mean square.
     """
 
     x: torch.Tensor
     weight: torch.Tensor | None
     eps: float
     layer_scale: torch.Tensor | None = None
+    groups: int = 1
 
 
 @dataclass

@@ -106,6 +106,11 @@ class SandwichBlockSpec:
     per-channel scale on what joins the residual stream.  ``feed_forward`` of ``None`` is a
     block of one sublayer.  The ``*_name`` fields are full tensor names (``None``: no layer
     scale); the prefixes end with a dot.
+
+    ``conv_taps > 0`` gives every sublayer an *input convolution*: what the sublayer reads, ``h``, is
+    replaced by ``h + conv(h)``, a causal convolution over time on every channel with the taps
+    ``conv1_name`` / ``conv2_name`` (``[width, conv_taps]``, the last column weighing the current token).
+    The last ``conv_taps - 1`` inputs are part of a request's state.
     """
 
     name: str
@@ -123,6 +128,9 @@ class SandwichBlockSpec:
     ffn_prefix: str | None = None
     norm_out2_name: str | None = None
     scale2_name: str | None = None
+    conv_taps: int = 0
+    conv1_name: str | None = None
+    conv2_name: str | None = None
     kind: str = "sandwich"
 
 
@@ -134,6 +142,11 @@ class SandwichBlock:
     A sublayer's output is left as a :class:`NormedBranch`; the norm in front of the next
     sublayer (this block's, the next block's, or the model's last norm) normalises it, scales
     it, adds it to the float32 residual stream and normalises the sum, in one kernel.
+
+    With input convolutions the block keeps state of its own beside its mixer's: one float32 record
+    ``[conv_taps - 1, width]`` per sublayer and request (``cache_need`` is then a dictionary, and so is the
+    view that ``forward`` is given).  Where the seat in front of a sublayer has no norm (``join``), the
+    convolution reads the float32 stream itself and its result is rounded once.
     """
 
     def __init__(self, spec: SandwichBlockSpec, tensors: dict[str, torch.Tensor], rt: Runtime):
@@ -151,6 +164,14 @@ class SandwichBlock:
         for norm in (self.norm_out1, self.norm_out2):
             if norm is not None and not hasattr(norm, "owed_norm_params"):
                 raise ValueError("the norm after a sublayer must hand out its weight and eps (owed_norm_params)")
+        self.rt = rt
+        self.conv1 = self.conv2 = None
+        if spec.conv_taps > 0:
+            if not 1 <= spec.conv_taps <= 8:
+                raise ValueError(f"an input convolution of {spec.conv_taps} taps is not taken (1 to 8)")
+            self.conv1 = tensors[spec.conv1_name].float().contiguous()
+            if spec.feed_forward is not None:
+                self.conv2 = tensors[spec.conv2_name].float().contiguous()
 
     @staticmethod
     def expected_tensors(spec: SandwichBlockSpec) -> dict[str, TensorReq]:
@@ -166,10 +187,25 @@ class SandwichBlock:
             out.update(NORMS.get(spec.norm_out2.kind).expected_tensors(spec.norm_out2, spec.norm_out2_name))
             if spec.scale2_name:
                 out[spec.scale2_name] = TensorReq((spec.norm_out2.dim,), role="vector")
+        if spec.conv_taps > 0:
+            width = spec.norm_out1.dim
+            out[spec.conv1_name] = TensorReq((width, spec.conv_taps), role="bias")
+            if spec.feed_forward is not None:
+                out[spec.conv2_name] = TensorReq((width, spec.conv_taps), role="bias")
         return out
 
     def cache_need(self):
-        return self.mixer.cache_need()
+        need = self.mixer.cache_need()
+        if self.spec.conv_taps <= 1:
+            return need
+        from ..cache.manager import StateNeed
+        tail = StateNeed((self.spec.conv_taps - 1, self.spec.norm_out1.dim), "float32")
+        out = {"conv1": tail}
+        if need is not None:
+            out["mixer"] = need
+        if self.conv2 is not None:
+            out["conv2"] = tail
+        return out
 
     def _parts(self) -> list:
         return [p for p in (self.norm_in1, self.mixer, self.norm_out1, self.norm_in2, self.feed_forward,
@@ -183,7 +219,8 @@ class SandwichBlock:
         return getattr(self.mixer, "prefill_heads", None)
 
     def weight_bytes(self) -> int:
-        extra = sum(t.numel() * t.element_size() for t in (self.scale1, self.scale2) if t is not None)
+        extra = sum(t.numel() * t.element_size() for t in (self.scale1, self.scale2, self.conv1, self.conv2)
+                    if t is not None)
         return weight_bytes(*self._parts()) + extra
 
     @property
@@ -193,14 +230,29 @@ class SandwichBlock:
     @staticmethod
     def _leave(x, norm, scale) -> NormedBranch:
         weight, eps = norm.owed_norm_params()
-        return NormedBranch(x, weight, eps, scale)
+        return NormedBranch(x, weight, eps, scale, getattr(norm, "groups", 1))
+
+    def _read(self, norm_in, taps, tail_view, resid, pending, step):
+        """What a sublayer reads: the rows of the seat in front of it, through the input convolution if
+        the block has one."""
+        if taps is None:
+            h = norm_in.add_norm(resid, pending)
+            return h.materialize() if isinstance(h, OwedNorm) else h
+        from ..csrc import ops
+        if hasattr(norm_in, "join"):
+            norm_in.join(resid, pending)
+            rows = resid
+        else:
+            rows = norm_in.add_norm(resid, pending)
+            rows = rows.materialize() if isinstance(rows, OwedNorm) else rows
+        tail = tail_view.records if tail_view is not None else None
+        return ops.short_conv(rows, taps, tail, step, dtype=self.rt.dtype, add_input=True)
 
     def forward(self, resid: torch.Tensor, pending, step, cache_view):
-        h = self.norm_in1.add_norm(resid, pending)
-        if isinstance(h, OwedNorm):
-            h = h.materialize()
-        pending = self._leave(self.mixer.forward(h, step, cache_view), self.norm_out1, self.scale1)
+        views = cache_view if isinstance(cache_view, dict) else {"mixer": cache_view}
+        h = self._read(self.norm_in1, self.conv1, views.get("conv1"), resid, pending, step)
+        pending = self._leave(self.mixer.forward(h, step, views.get("mixer")), self.norm_out1, self.scale1)
         if self.feed_forward is not None:
-            h = self.norm_in2.add_norm(resid, pending)
+            h = self._read(self.norm_in2, self.conv2, views.get("conv2"), resid, pending, step)
             pending = self._leave(self.feed_forward.forward(h, step), self.norm_out2, self.scale2)
         return resid, pending

@@ -98,3 +98,90 @@ class SwiGLU:
                 act = torch.empty((n, self.spec.intermediate_size), dtype=h.dtype, device=h.device)
                 ops.swiglu(gate_up, act, block=self.block, activation=self.spec.activation)
         return linear(act, self.w_down, err=err, then_norm=then_norm, chain=chain)
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """A mixture of ``num_experts`` gated units of inner size ``intermediate_size`` of which every token uses
+    ``top``.  The experts form ``num_groups`` equal groups of neighbours and only experts of the ``keep_groups``
+    best groups can be chosen (``num_groups = keep_groups = 1``: no restriction).  ``correction``: a learned
+    number per expert that is added to the scores for the choice only.  The ``*_name`` fields are the
+    tensors' names after the part's prefix; expert ``e``'s matrices lie under ``expert_prefix.format(e)``."""
+
+    hidden_size: int
+    intermediate_size: int
+    num_experts: int
+    top: int
+    num_groups: int = 1
+    keep_groups: int = 1
+    correction: bool = True
+    activation: str = "silu"
+    router_name: str = "router"
+    correction_name: str = "correction"
+    expert_prefix: str = "e{}."
+    gate_name: str = "gate"
+    up_name: str = "up"
+    down_name: str = "down"
+    kind: str = "moe"
+
+
+@FEED_FORWARDS.register("moe")
+class MixtureOfExperts:
+    """Router scores are sigmoids of 32-bit logits, ``s = sigmoid(W_r h)``; the choice is made on
+    ``s + correction``: a group's score is the sum of its two largest choice scores, experts outside the best
+    groups cannot be chosen, and the ``top`` largest of the rest are; the weights are the chosen experts'
+    plain scores, not renormalised; the output is the weighted sum of the chosen experts'
+    ``W_down (act(W_gate h) * (W_up h))``.  Experts have no biases.
+
+    The experts' matrices are stacked ``[experts, ...]`` at load.  A step's (token, choice) pairs are laid
+    out expert by expert on the device, so nothing is read back and a step of single tokens can be
+    replayed from a CUDA graph; the products run over tiles of one expert's rows (``csrc/moe.cu``).  The
+    result is float32 and does not depend on what else is in the batch.
+    """
+
+    GRAPH_SAFE = True
+
+    def __init__(self, spec: MoESpec, prefix: str, tensors: dict[str, torch.Tensor], rt: Runtime):
+        if spec.activation not in ops.GLU_ACTIVATIONS:
+            raise ValueError(f"unknown activation {spec.activation!r}; known: {', '.join(ops.GLU_ACTIVATIONS)}")
+        if spec.num_experts % spec.num_groups or not 1 <= spec.keep_groups <= spec.num_groups:
+            raise ValueError(f"{spec.num_experts} experts do not form {spec.num_groups} equal groups of which "
+                             f"{spec.keep_groups} are kept")
+        if not 1 <= spec.top <= spec.keep_groups * (spec.num_experts // spec.num_groups):
+            raise ValueError(f"{spec.top} experts cannot be chosen from {spec.keep_groups} groups of "
+                             f"{spec.num_experts // spec.num_groups}")
+        self.spec = spec
+        self.rt = rt
+        self.router = tensors[prefix + spec.router_name].float().contiguous()
+        self.correction = tensors[prefix + spec.correction_name].contiguous() if spec.correction else None
+        stack = lambda name: torch.stack([tensors[prefix + spec.expert_prefix.format(e) + name]
+                                          for e in range(spec.num_experts)]).contiguous()
+        self.w_gate, self.w_up, self.w_down = stack(spec.gate_name), stack(spec.up_name), stack(spec.down_name)
+
+    @staticmethod
+    def expected_tensors(spec: MoESpec, prefix: str) -> dict[str, TensorReq]:
+        h, i = spec.hidden_size, spec.intermediate_size
+        out = {}
+        for e in range(spec.num_experts):
+            p = prefix + spec.expert_prefix.format(e)
+            out[p + spec.gate_name] = TensorReq((i, h))
+            out[p + spec.up_name] = TensorReq((i, h))
+            out[p + spec.down_name] = TensorReq((h, i))
+        out[prefix + spec.router_name] = TensorReq((spec.num_experts, h), role="matrix_f32")
+        if spec.correction:
+            out[prefix + spec.correction_name] = TensorReq((spec.num_experts,), role="bias")
+        return out
+
+    def weight_bytes(self) -> int:
+        """What a step of one token reads: the router and ``top`` experts (a large step reads all)."""
+        per_expert = tensor_bytes(self.w_gate, self.w_up, self.w_down) // self.spec.num_experts
+        return tensor_bytes(self.router, self.correction) + self.spec.top * per_expert
+
+    def forward(self, h, step):
+        spec = self.spec
+        if isinstance(h, OwedNorm):
+            h = h.materialize()
+        routing = ops.moe_route(h, self.router, self.correction, top=spec.top, n_groups=spec.num_groups,
+                                keep=spec.keep_groups)
+        out = ops.moe_experts(h, routing, self.w_gate, self.w_up, self.w_down, activation=spec.activation)
+        return out.unsqueeze(0)         # float32 sums, one part: the consuming norm reads them as they are

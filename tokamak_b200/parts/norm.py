@@ -58,7 +58,7 @@ class RMSNorm:
             n = rows.numel() if rows is not None else resid.shape[0]
             out = torch.empty((n, self.spec.dim), dtype=self.rt.dtype, device=resid.device)
             ops.branch_norm_add(resid, delta.x, delta.weight, delta.layer_scale, delta.eps, self.weight, out,
-                                self.spec.eps, rows)
+                                self.spec.eps, rows, branch_groups=delta.groups)
             return out
         if isinstance(delta, OwedNorm):
             if delta.norm is self:
@@ -120,13 +120,24 @@ class CastNorm:
     def weight_bytes(self) -> int:
         return 0
 
+    def join(self, resid: torch.Tensor, delta) -> None:
+        """Only the first half: the pending branch joins the float32 stream, nothing is handed on (for a
+        block whose sublayer reads the stream through a kernel of its own)."""
+        if isinstance(delta, NormedBranch):
+            ops.branch_norm_add(resid, delta.x, delta.weight, delta.layer_scale, delta.eps, None, None, 0.0, None,
+                                branch_groups=delta.groups)
+        elif delta is not None and not isinstance(delta, OwedNorm):
+            from .base import sum_parts
+            resid.add_(sum_parts(delta, torch.float32))
+
     def add_norm(self, resid: torch.Tensor, delta, rows: torch.Tensor | None = None):
         if isinstance(delta, OwedNorm):
             delta = None        # its branch is in the stream already
         if isinstance(delta, NormedBranch):
             n = rows.numel() if rows is not None else resid.shape[0]
             out = torch.empty((n, self.spec.dim), dtype=self.rt.dtype, device=resid.device)
-            ops.branch_norm_add(resid, delta.x, delta.weight, delta.layer_scale, delta.eps, None, out, 0.0, rows)
+            ops.branch_norm_add(resid, delta.x, delta.weight, delta.layer_scale, delta.eps, None, out, 0.0, rows,
+                                branch_groups=delta.groups)
             return out
         if delta is not None:
             from .base import sum_parts
@@ -137,3 +148,59 @@ class CastNorm:
                 return (resid.index_select(0, rows.long()) + delta.index_select(0, rows.long())).to(self.rt.dtype)
         x = resid if rows is None else resid.index_select(0, rows.long())
         return x.to(self.rt.dtype, copy=True)
+
+
+@dataclass(frozen=True)
+class GroupRMSNormSpec:
+    """An RMS norm in ``groups`` equal consecutive parts of the row: every part is divided by its own
+    root mean square, the whole is multiplied by one weight per channel."""
+
+    dim: int
+    eps: float
+    groups: int
+    kind: str = "rmsnorm_groups"
+
+
+@NORMS.register("rmsnorm_groups")
+class GroupRMSNorm:
+    """``w * x / sqrt(mean_part(x^2) + eps)`` with the mean taken over the part of the row that the channel
+    lies in; statistics are float32.  Behind a sublayer it rides in the :class:`NormedBranch` (``groups``);
+    in front of one, or as a model's last norm, it joins the pending branch and normalises in one kernel."""
+
+    GRAPH_SAFE = True
+
+    def __init__(self, spec: GroupRMSNormSpec, name: str, tensors: dict[str, torch.Tensor], rt: Runtime):
+        if spec.groups < 1 or spec.dim % spec.groups:
+            raise ValueError(f"a row of {spec.dim} does not split into {spec.groups} equal groups")
+        self.spec = spec
+        self.rt = rt
+        self.weight = tensors[name]
+        self.groups = spec.groups
+
+    @staticmethod
+    def expected_tensors(spec: GroupRMSNormSpec, name: str) -> dict[str, TensorReq]:
+        return {name: TensorReq((spec.dim,), role="vector")}
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def owed_norm_params(self) -> tuple[torch.Tensor, float]:
+        return self.weight, self.spec.eps
+
+    def add_norm(self, resid: torch.Tensor, delta, rows: torch.Tensor | None = None):
+        if isinstance(delta, OwedNorm):
+            delta = None        # its branch is in the stream already
+        n = rows.numel() if rows is not None else resid.shape[0]
+        out = torch.empty((n, self.spec.dim), dtype=self.rt.dtype, device=resid.device)
+        if isinstance(delta, NormedBranch):
+            ops.branch_norm_add(resid, delta.x, delta.weight, delta.layer_scale, delta.eps, self.weight, out,
+                                self.spec.eps, rows, branch_groups=delta.groups, next_groups=self.spec.groups)
+            return out
+        if delta is not None:
+            from .base import sum_parts
+            if rows is not None:
+                raise ValueError("a plain branch cannot join selected rows only")
+            resid.add_(sum_parts(delta, torch.float32))
+        ops.branch_norm_add(resid, None, None, None, 0.0, self.weight, out, self.spec.eps, rows,
+                            next_groups=self.spec.groups)
+        return out

@@ -9,7 +9,7 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import POSITIONS, Runtime
+from .base import POSITIONS, Runtime, TensorReq
 
 
 @dataclass(frozen=True)
@@ -147,3 +147,38 @@ class NoPosition:
 
     def rotary_table(self, step) -> tuple[torch.Tensor | None, int]:
         return None, 0
+
+
+@dataclass(frozen=True)
+class LearnedPositionSpec:
+    """An absolute encoding: row ``position`` of a learned table ``[max_positions, hidden_size]`` joins the
+    embedded token, times ``scale``."""
+
+    max_positions: int
+    hidden_size: int
+    name: str = "pos"
+    scale: float = 1.0
+    kind: str = "learned_absolute"
+
+
+@POSITIONS.register("learned_absolute")
+class LearnedPosition:
+    """For the model's ``embedding_position`` seat: ``x[t] += scale * table[position[t]]`` in the float32
+    stream (the embedding's gather kernel, accumulating).  A position beyond the table is reported through
+    the step's error word."""
+
+    GRAPH_SAFE = True
+
+    def __init__(self, spec: LearnedPositionSpec, tensors: dict, rt: Runtime):
+        self.spec = spec
+        self.table = tensors[spec.name]
+
+    @staticmethod
+    def expected_tensors(spec: LearnedPositionSpec) -> dict:
+        return {spec.name: TensorReq((spec.max_positions, spec.hidden_size))}
+
+    def weight_bytes(self) -> int:
+        return 0          # read by row
+
+    def add_to_embedding(self, resid: torch.Tensor, step) -> None:
+        ops.embed_gather(self.table, step.positions, resid, step.err, scale=self.spec.scale, accumulate=True)

@@ -62,7 +62,7 @@ def target_dtype(req: TensorReq, stored: torch.dtype, engine_dtype: torch.dtype)
     float32 (exact for bfloat16 and for 32-bit storage), integer tables are int32."""
     if req.role == "int_table" or not stored.is_floating_point:
         return torch.int32
-    if req.role in ("vector", "bias", "fraction"):
+    if req.role in ("vector", "bias", "fraction", "matrix_f32"):
         return torch.float32
     return engine_dtype
 

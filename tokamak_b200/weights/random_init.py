@@ -36,6 +36,9 @@ def random_tensors(expected: Mapping[str, TensorReq], seed: int, std: float = 0.
             t = 0.5 * torch.randn(req.shape, generator=gen, dtype=torch.float32, device=device)
         elif req.role == "fraction":
             t = 0.2 + 0.6 * torch.rand(req.shape, generator=gen, dtype=torch.float32, device=device)
+        elif req.role == "matrix_f32":
+            # values that the checkpoint's 16-bit storage holds exactly
+            t = (std * torch.randn(req.shape, generator=gen, dtype=torch.float32, device=device)).to(dtype).float()
         elif req.role == "int_table":
             t = torch.zeros(req.shape, dtype=torch.int32, device=device)
         else:
