@@ -210,10 +210,34 @@ def route(h, router, correction, top, n_groups, keep):
     return chosen, s.gather(1, chosen)
 
 
-def moe(h, w, m):
+def route_margin(h, router, correction, top, n_groups, keep) -> torch.Tensor:
+    """How far every token is from another choice, ``[T]``: the smaller of the gap between the last group
+    kept and the best one left out and the gap between the last expert chosen and the best one left out
+    among the kept groups (infinite where nothing is left out)."""
+    choice = torch.sigmoid(h @ router.T) + correction
+    T, E = choice.shape
+    size = E // n_groups
+    group_score = choice.view(T, n_groups, size).topk(min(2, size), dim=-1).values.sum(-1)
+    ranked = group_score.sort(-1, descending=True)
+    margin = torch.full((T,), math.inf, dtype=F64)
+    if keep < n_groups:
+        margin = ranked.values[:, keep - 1] - ranked.values[:, keep]
+    allowed = torch.zeros(T, n_groups, dtype=torch.bool)
+    allowed.scatter_(1, ranked.indices[:, :keep], True)
+    masked = torch.where(allowed[:, :, None].expand(T, n_groups, size).reshape(T, E), choice,
+                         torch.full_like(choice, -math.inf)).sort(-1, descending=True).values
+    if top < keep * size:
+        margin = torch.minimum(margin, masked[:, top - 1] - masked[:, top])
+    return margin
+
+
+def moe(h, w, m, margins_out: list | None = None):
     """A mixture of silu-gated experts; the output is the weighted sum of the chosen experts'."""
     r = m["router"]
     h = ROUND(h)
+    if margins_out is not None:
+        margins_out.append(route_margin(h, w["router"], w["correction"], int(r["top"]), int(r["groups"]["count"]),
+                                        int(r["groups"]["keep"])))
     chosen, weights = route(h, w["router"], w["correction"], int(r["top"]), int(r["groups"]["count"]),
                             int(r["groups"]["keep"]))
     out = torch.zeros_like(h)
@@ -236,9 +260,11 @@ def _sub(tensors: dict, prefix: str) -> dict:
     return {k[len(prefix):]: t for k, t in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg: dict, tensors: dict, tokens, round_to: torch.dtype | None = None, layers_out: list | None = None):
+def forward(cfg: dict, tensors: dict, tokens, round_to: torch.dtype | None = None, layers_out: list | None = None,
+            margins_out: list | None = None):
     """Float64 logits ``[T, vocab]`` of one whole sequence; ``layers_out`` collects the stream after
-    every layer.  ``round_to`` rounds where an engine with 16-bit activations rounds."""
+    every layer, ``margins_out`` every router's distance from another choice, token by token.  ``round_to``
+    rounds where an engine with 16-bit activations rounds."""
     global ROUND
     keep = ROUND
     if round_to is not None:
@@ -255,7 +281,7 @@ def forward(cfg: dict, tensors: dict, tokens, round_to: torch.dtype | None = Non
             x = x + group_norm(MIXERS[lay["type"]](h, _sub(w, p + "mix."), lay["mixer"], eps), w[p + "norm1"], groups, eps)
             if lay.get("mlp") is not None:
                 h = input_conv(x, w[p + "canon2"])
-                x = x + group_norm(moe(h, _sub(w, p + "mlp."), lay["mlp"]), w[p + "norm2"], groups, eps)
+                x = x + group_norm(moe(h, _sub(w, p + "mlp."), lay["mlp"], margins_out), w[p + "norm2"], groups, eps)
             if layers_out is not None:
                 layers_out.append(x.clone())
         return ROUND(group_norm(x, w["final.norm"], groups, eps)) @ w["head"].T
@@ -268,3 +294,13 @@ def load_folder(folder) -> tuple[dict, dict]:
     from safetensors.torch import load_file
     folder = Path(folder)
     return json.loads((folder / "config.json").read_text()), load_file(str(folder / "model.safetensors"))
+
+
+def greedy_generate(cfg: dict, tensors: dict, prompt, n: int) -> list[int]:
+    """The ``n`` tokens that always taking the largest logit gives."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        tok = int(forward(cfg, tensors, seq)[-1].argmax())
+        out.append(tok)
+        seq.append(tok)
+    return out

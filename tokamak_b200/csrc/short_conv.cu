@@ -50,8 +50,8 @@ __global__ void short_conv_kernel(ShortConvParams p) {
   const int r = p.tok_req[t];
   if (r < 0 || r >= p.n_reqs) { set_error(p.err, kErrRequest, t, r, p.n_reqs); return; }
   const int slot = p.req_slot[r], q0 = p.req_q_start[r];
-  if (slot < 0 || slot >= p.n_slots || q0 > t) { set_error(p.err, kErrRequest, t, slot, q0); return; }
   const int K = p.taps_n, i = t - q0;
+  if ((K > 1 && (slot < 0 || slot >= p.n_slots)) || q0 > t) { set_error(p.err, kErrRequest, t, slot, q0); return; }
   float* tail = p.tail + (size_t)slot * (K - 1) * p.channels + c;
   const float* w = p.taps + (size_t)c * K;
   float x[kConvMaxTaps];

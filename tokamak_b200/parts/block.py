@@ -249,7 +249,9 @@ class SandwichBlock:
         return ops.short_conv(rows, taps, tail, step, dtype=self.rt.dtype, add_input=True)
 
     def forward(self, resid: torch.Tensor, pending, step, cache_view):
-        views = cache_view if isinstance(cache_view, dict) else {"mixer": cache_view}
+        # with input convolutions of more than one tap the view is this block's dictionary (see cache_need);
+        # otherwise it is the mixer's own, which may be a dictionary too
+        views = cache_view if self.spec.conv_taps > 1 else {"mixer": cache_view}
         h = self._read(self.norm_in1, self.conv1, views.get("conv1"), resid, pending, step)
         pending = self._leave(self.mixer.forward(h, step, views.get("mixer")), self.norm_out1, self.scale1)
         if self.feed_forward is not None:
