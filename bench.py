@@ -1146,9 +1146,260 @@ def logivik_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
     return rows
 
 
+# ------------------------------------------------------------------------------------------------
+# --design tarivik: the Tarivik design beside a Ketalix model of equal layer sizes (the engine's
+# closest other design: paged attention layers and recurrent layers on the same recurrence kernel in turn)
+
+def tarivik_config(s: dict) -> dict:
+    """Parallel (chunked attention beside a state-space half), HGRN2, parallel, mLSTM, and again; every layer with
+    a mixture of 8 experts of which 2 are used, together as wide as the twin's feed-forward.  Attention heads
+    as the twin's, chunks as long as its window; the state-space half has width / 64 heads of 64 channels and a
+    state of 128 rows; the other recurrent layers have the twin's state (width / 256 heads, 128 x 256)."""
+    w, d = s["width"], s["dim"]
+    left = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5,
+            "mask": {"size": s["window"]}}
+    right = {"heads": w // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 2}
+    par = {"left": left, "right": right, "left_scale": 0.8, "right_scale": 0.5}
+    rec = {"heads": w // 256, "dim": 128, "vdim": 256}
+    mlp = {"kind": "moe", "expert": {"ff": s["ff"] // 2},
+           "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    order = [("parallel", par), ("hgrn2", rec), ("parallel", par), ("mlstm", dict(rec, gate_cap=15.0))]
+    layers = [{"type": order[i % 4][0], "mixer": order[i % 4][1], "mlp": mlp} for i in range(s["layers"])]
+    return {"architecture": "Tarivik", "vocab": s["vocab"], "width": w, "max_positions": 32768,
+            "norm": {"eps": 1e-6, "groups": 4}, "canon": {"taps": 4}, "layers": layers}
+
+
+def tarivik_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> list[dict]:
+    """Every kernel of the design alone, beside the like kernel of the Ketalix path at the same shape:
+    time, achieved bytes or flops per second, and the fraction of the measured peak."""
+    import torch
+    from types import SimpleNamespace
+    from tokamak_b200.csrc import ops
+    from tokamak_b200.parts.attention import paged_attention
+    from tokamak_b200.cache.device import KVView
+    dev = "cuda"
+    gen = torch.Generator(device=dev).manual_seed(0)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    err = torch.zeros(4, dtype=torch.int32, device=dev)
+    hq, hkv, d, page, chunk, width = s["heads"], s["kv_heads"], s["dim"], 16, s["window"], s["width"]
+    ffe, experts, top = s["ff"] // 2, 8, 2
+    bf = lambda *shape: torch.randn(shape, device=dev, generator=gen).bfloat16()
+    f32 = lambda *shape: torch.randn(shape, device=dev, generator=gen)
+    rows = []
+
+    def row(kernel, like, us, us_like, nbytes=0, flops=0.0, like_bytes=0, like_flops=0.0, note=""):
+        r = {"kernel": kernel, "like": like, "us": round(us, 1), "like_us": round(us_like, 1) if us_like else None}
+        for name, t, fl, nb in (("", us, flops, nbytes), ("like_", us_like, like_flops or flops, like_bytes or nbytes)):
+            if not t:
+                continue
+            if fl:
+                r[name + "bf16_frac"] = round(fl / (t * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
+            elif nb:
+                r[name + "hbm_frac"] = round(nb / (t * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+        if note:
+            r["note"] = note
+        rows.append(r)
+
+    def step_of(n, n_req, start):
+        per = n // n_req
+        return SimpleNamespace(
+            positions=i32([start + i for _ in range(n_req) for i in range(per)]),
+            tok_req=i32([r for r in range(n_req) for _ in range(per)]), req_q_start=i32([r * per for r in range(n_req)]),
+            req_q_len=i32([per] * n_req), req_kv_len=i32([start + per] * n_req), req_slot=i32(list(range(n_req))),
+            err=err, max_q_len=per, n_tokens=n, n_reqs=n_req, scratch={}, host_q_start=[r * per for r in range(n_req)],
+            host_q_len=[per] * n_req, host_kv_len=[start + per] * n_req, host_slot=list(range(n_req)),
+            max_kv_len=start + per)
+
+    sinks, slopes = f32(hq), torch.pow(2.0, -8.0 * torch.arange(1, hq + 1, device=dev) / hq).float()
+    cases = (("prompt", tokens, 1, 0), ("single tokens", batch, batch, ctx - 1))
+    # ---- chunked attention with distance bias and sinks; the twin's has a window, a cap and sinks
+    for name, n, n_req, start in cases:
+        single = n_req > 1
+        step = step_of(n, n_req, start)
+        pages_req = -(-(start + n // n_req) // page)
+        kc, vc = bf(n_req * pages_req, hkv, page, d), bf(n_req * pages_req, hkv, page, d)
+        table = torch.randperm(n_req * pages_req, device=dev, generator=gen).to(torch.int32).view(n_req, pages_req)
+        q = bf(n, hq, d)
+        out = torch.empty_like(q)
+        view = KVView(kc, vc, table, page, None)
+        if single:
+            keys = n * ((start % chunk) + 1)
+            like_keys = n * min(start + 1, chunk)
+            n_splits = ops.decode_splits(n, hkv, min(ctx, chunk))
+            scratch = torch.empty(n * hq * n_splits * (d + 2), dtype=torch.float32, device=dev)
+            it = i32(list(range(n)))
+            like = lambda: ops.attention_decode(q, out, kc, vc, it, step.positions, it, it, table, err, scale=d ** -0.5,
+                                                window=chunk, n_splits=n_splits, scratch=scratch, softcap=30.0, sinks=sinks)
+        else:
+            keys = sum((i % chunk) + 1 for i in range(n))
+            like_keys = sum(min(i + 1, chunk) for i in range(n))
+            rec, n_parts, n_split = ops.prefill_tc_records([0], [n], [n], [0], heads=hq, sms=ops.sm_count(q.device))
+            items = ops.PrefillItems(torch.from_numpy(rec).to(dev), n_parts, n_split)
+            like = lambda: ops.attention_prefill_tc(q, out, kc, vc, items, table, err, scale=d ** -0.5, window=chunk,
+                                                    softcap=30.0, sinks=sinks)
+        mine = lambda: paged_attention(q, out, view, step, scale=d ** -0.5, window=None, sinks=sinks, chunk=chunk,
+                                       slopes=slopes)
+        mine()
+        if single:
+            row(f"chunked attention (distance bias, sink), {name}", "windowed attention (cap, sink), single tokens",
+                _time_us(mine, graph=True), _time_us(like, graph=True), nbytes=2 * hkv * keys * d * 2 + 2 * q.numel() * 2,
+                like_bytes=2 * hkv * like_keys * d * 2 + 2 * q.numel() * 2,
+                note=f"the last token of a chunk would see {chunk} keys; at position {start} it sees {(start % chunk) + 1}")
+        else:
+            row(f"chunked attention (distance bias, sink), {name}", "windowed attention (cap, sink), prompt",
+                _time_us(mine, iters=5), _time_us(like), flops=4.0 * keys * hq * d, like_flops=4.0 * like_keys * hq * d)
+        # ---- biases, whole-row norms of q and k, page write
+        proj = bf(n, (2 * hq + 2 * hkv) * d)
+        qb, kb, vb = f32(hq * d), f32(hkv * d), f32(hkv * d)
+        qn, kn = f32(hq * d), f32(hkv * d)
+        rn = lambda: ops.qkv_rownorm(proj, q, kc, vc, step, table, q_off=0, k_off=hq * d, v_off=(hq + hkv) * d, q_bias=qb,
+                                     k_bias=kb, v_bias=vb, q_norm=qn, k_norm=kn, eps=1e-6)
+        qkv = bf(n, (hq + 2 * hkv) * d)
+        inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev)
+        rot = ops.rope_table(step.positions, inv_freq)
+        vf, lam = f32(n, hkv * d), torch.full((1,), 0.3, device=dev)
+        pairs = lambda: ops.qkv_pairs(qkv, q, kc, vc, step.positions, step.tok_req, step.req_slot, table, rot, err,
+                                      n_q_heads=hq, n_kv_heads=hkv, rotary_dim=d, unit_norm_eps=1e-6, v_first_in=vf,
+                                      v_lambda=lam, req_q_len=step.req_q_len, req_kv_len=step.req_kv_len)
+        nb = 2 * (hq + 2 * hkv) * d * n * 2
+        row(f"biases + norms over whole q and k + page write, {name}",
+            f"pair rotation + unit norm + value blend + page write, {name}", _time_us(rn, graph=single),
+            _time_us(pairs, graph=single), nbytes=nb, like_bytes=nb + vf.numel() * 4)
+        att, gproj = bf(n, hq * d), bf(n, (2 * hq + 2 * hkv) * d)
+        wide = torch.empty(n, hq * d + width, dtype=torch.bfloat16, device=dev)
+        row(f"output gate + branch factor into the stacked rows, {name}", None,
+            _time_us(lambda: ops.gate_scale(att, gproj, (hq + 2 * hkv) * d, out=wide[:, :hq * d], scale=0.8), graph=single),
+            0.0, nbytes=3 * n * hq * d * 2)
+        # ---- the block's seats: join with a norm in groups, then the input convolution on the stream
+        resid, branch = f32(n, width), bf(n, width)
+        w1 = torch.ones(width, device=dev)
+        normed = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
+        row(f"output norm in groups + residual, {name}", f"output norm + layer scale + residual + input norm, {name}",
+            _time_us(lambda: ops.branch_norm_add(resid, branch, w1, None, 1e-6, None, None, branch_groups=4), graph=single),
+            _time_us(lambda: ops.branch_norm_add(resid, branch, w1, w1, 1e-6, w1, normed, 1e-6), graph=single),
+            nbytes=n * width * (2 + 8), like_bytes=n * width * (2 + 8 + 2))
+        taps4, tail = f32(width, 4) * 0.3, torch.zeros(n_req, 3, width, device=dev)
+        row(f"input convolution on the float32 stream, {name}", None,
+            _time_us(lambda: ops.short_conv(resid, taps4, tail, step, dtype=torch.bfloat16, add_input=True), graph=single),
+            0.0, nbytes=n * width * (4 + 2) + (2 * tail.numel() * 4 if single else 0))
+        # ---- mixture of experts against the twin's gated unit of the same active width
+        h = bf(n, width)
+        router, corr = f32(experts, width) * 0.05, f32(experts) * 0.05
+        wg, wu = bf(experts, ffe, width) * width ** -0.5, bf(experts, ffe, width) * width ** -0.5
+        wd = bf(experts, width, ffe) * ffe ** -0.5
+        route = lambda: ops.moe_route(h, router, corr, top=top, n_groups=4, keep=2, padded=True)
+        routing = route()
+        row(f"router (scores, groups, choice, tiles), {name}", None, _time_us(route, graph=False), 0.0,
+            nbytes=n * width * 2 + experts * width * 4)
+        wgu_dense = bf(2 * top * ffe, width) * width ** -0.5
+        wd_dense = bf(width, top * ffe) * (top * ffe) ** -0.5
+        from tokamak_b200.parts.base import linear
+
+        def dense():
+            if ops.pair_gemm_takes(n, 2 * top * ffe, width, fused=True):
+                a = ops.gemm_pair(h, wgu_dense, err, swiglu=True)
+            else:
+                gu = linear(h, wgu_dense, err=err)
+                a = torch.empty(n, top * ffe, dtype=torch.bfloat16, device=dev)
+                ops.swiglu(gu, a, block=ops.SWIGLU_TILE_BLOCK)
+            y = linear(a, wd_dense, err=err)
+            ops.flush_chains()
+            return y
+        used = len(set(routing.chosen.flatten().tolist()))
+        wgu = ops.moe_stack_gate_up(wg, wu)
+        moe = lambda: ops.moe_experts_tc(h, routing, wgu, wd, err)
+        flops = 2.0 * n * top * 3 * ffe * width
+        if single:
+            row(f"experts (gate, up, down, weighted sum), {name}", "dense gated unit of the same active width",
+                _time_us(moe, graph=True), _time_us(dense, graph=True),
+                nbytes=used * 3 * ffe * width * 2, like_bytes=top * 3 * ffe * width * 2,
+                note=f"{used} of {experts} experts are read by the {n} tokens")
+        else:
+            row(f"experts (gate, up, down, weighted sum), {name}", "dense gated unit of the same active width",
+                _time_us(moe), _time_us(dense), flops=flops)
+        # ---- the recurrent layers: inputs, recurrence, output stage, beside gated linear attention's
+        gh, gk, gv, rk = width // 256, 128, 256, 16
+        sh, sn, sv = width // 64, 128, 64
+        gproj = bf(n, 2 * gh * gk + 2 * gh * gv + rk) * 0.5
+        w2a, gbias = bf(gh * gk, rk) * 0.1, f32(gh * gk)
+        gprep = lambda: ops.gla_prepare(gproj, 0, gh * gk, 2 * gh * gk, 2 * gh * gk + 2 * gh * gv, w2a, gbias, heads=gh,
+                                        key_dim=gk, value_dim=gv, tau=16.0, q_scale=gk ** -0.5)
+        gstate = torch.zeros(n_req, gh, gk, gv, device=dev)
+        gp = gprep()
+        gscan = lambda: ops.gla_scan(gp, gstate, step.req_q_start, step.req_q_len, step.req_slot, err)
+        go = gscan()
+        us_gscan, us_gprep = _time_us(gscan, graph=single), _time_us(gprep, graph=single)
+        nw = torch.ones(gv, device=dev)
+        us_gout = _time_us(lambda: ops.gla_out(go, gproj, 2 * gh * gk + gh * gv, nw, 1e-6, torch.bfloat16), graph=single)
+        gla_in = n * (2 * gh * gk + gh * gv + rk) * 2 + gp.numel() * 4
+
+        def scan_row(kind, prep, state, heads, dk, dv, like_us):
+            scan = lambda: ops.gla_scan(prep, state, step.req_q_start, step.req_q_len, step.req_slot, err)
+            o = scan()
+            us = _time_us(scan, graph=single)
+            r = {"kernel": f"{kind} recurrence, {name}", "like": f"gla recurrence, {name}", "us": round(us, 1),
+                 "like_us": round(like_us, 1),
+                 "hbm_frac": round((2 * state.numel() * 4 + prep.numel() * 4 + o.numel() * 4) / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
+                 "like_hbm_frac": round((2 * gstate.numel() * 4 + gp.numel() * 4 + go.numel() * 4) / (like_us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
+                 "fp32_tflops": round(4.0 * n * heads * dk * dv / (us * 1e-6) / 1e12, 2),
+                 "like_fp32_tflops": round(4.0 * n * gh * gk * gv / (like_us * 1e-6) / 1e12, 2),
+                 "note": "the same kernel: float32 on the CUDA cores, token by token"}
+            rows.append(r)
+            return o
+        # HGRN2
+        hproj, fb, lower = bf(n, 2 * gh * gk + gh * gv) * 0.5, f32(gh * gk), torch.rand(gh * gk, device=dev, generator=gen) * 0.9
+        hprep = lambda: ops.hgrn2_prepare(hproj, fb, lower, dtype=torch.bfloat16, q_off=0, f_off=gh * gk, v_off=2 * gh * gk,
+                                          heads=gh, key_dim=gk, value_dim=gv)
+        hp = hprep()
+        row(f"hgrn2 float32 inputs (silu q, bounded gate, 1 - gate, v), {name}", f"gla float32 inputs, {name}",
+            _time_us(hprep, graph=single), us_gprep, nbytes=hproj.numel() * 2 + hp.numel() * 4, like_bytes=gla_in)
+        ho = scan_row("hgrn2", hp, torch.zeros(n_req, gh, gk, gv, device=dev), gh, gk, gv, us_gscan)
+        row(f"hgrn2 output norm, {name}", f"gla output norm + gate, {name}",
+            _time_us(lambda: ops.gla_out(ho, None, 0, nw, 1e-6, torch.bfloat16), graph=single), us_gout,
+            nbytes=n * gh * gv * (4 + 2), like_bytes=n * gh * gv * (4 + 2 + 2))
+        # mLSTM
+        mproj = bf(n, 2 * gh * gk + 2 * gh * gv + 2 * gh) * 0.5
+        ib, fbm, mstate = f32(gh), f32(gh) + 3.0, torch.zeros(n_req, gh, device=dev)
+        mprep = lambda: ops.mlstm_prepare(mproj, ib, fbm, mstate, step, dtype=torch.bfloat16, q_off=0, k_off=gh * gk,
+                                          v_off=2 * gh * gk, i_off=2 * gh * gk + 2 * gh * gv, f_off=2 * gh * gk + 2 * gh * gv + gh,
+                                          heads=gh, key_dim=gk, value_dim=gv, cap=15.0, q_scale=gk ** -0.5)
+        mp, mg = mprep()
+        row(f"mlstm float32 inputs (gates, running maximum, scaled q, k, v | 1), {name}", f"gla float32 inputs, {name}",
+            _time_us(mprep, graph=single, iters=5 if not single else 20), us_gprep,
+            nbytes=n * (2 * gh * gk + gh * gv + 2 * gh) * 2 + mp.numel() * 4, like_bytes=gla_in)
+        mo = scan_row("mlstm", mp, torch.zeros(n_req, gh, gk, gv + 1, device=dev), gh, gk, gv + 1, us_gscan)
+        nwm = torch.ones(gh * gv, device=dev)
+        row(f"mlstm normaliser + unit norm + gate, {name}", f"gla output norm + gate, {name}",
+            _time_us(lambda: ops.mlstm_out(mo, mg, mproj, 2 * gh * gk + gh * gv, nwm, 1e-6, torch.bfloat16), graph=single),
+            us_gout, nbytes=n * gh * gv * (4 + 2 + 2))
+        # the state-space half
+        inner, cch = sh * sv, sh * sv + 2 * sn
+        sproj = bf(n, inner + cch + sh) * 0.5
+        taps_s, cb, ctail = f32(cch, 4) * 0.3, f32(cch) * 0.1, torch.zeros(n_req, 3, cch, device=dev)
+        sconv = lambda: ops.short_conv(sproj, taps_s, ctail, step, dtype=torch.bfloat16, in_off=inner, channels=cch,
+                                       bias=cb, silu=True, out_f32=True)
+        xbc = sconv()
+        row(f"state-space convolution + silu, {name}", None, _time_us(sconv, graph=single), 0.0, nbytes=n * cch * (2 + 4))
+        dtb, alog, skip = f32(sh) * 0.5, f32(sh) * 0.5 - 1.0, f32(sh)
+        sprep = lambda: ops.ssd_prepare(xbc, sproj, inner + cch, dtb, alog, dtype=torch.bfloat16, heads=sh, groups=1,
+                                        state=sn, value_dim=sv)
+        sp = sprep()
+        row(f"state-space float32 inputs (dt, decay, B, C, dt x), {name}", f"gla float32 inputs, {name}",
+            _time_us(sprep, graph=single), us_gprep, nbytes=xbc.numel() * 4 + sp.numel() * 4, like_bytes=gla_in)
+        so = scan_row("state-space", sp, torch.zeros(n_req, sh, sn, sv, device=dev), sh, sn, sv, us_gscan)
+        nws = torch.ones(inner, device=dev)
+        row(f"state-space skip + gate + norm in groups + branch factor, {name}", f"gla output norm + gate, {name}",
+            _time_us(lambda: ops.ssd_out(so, xbc, sproj, 0, skip, nws, 2, 1e-6, torch.bfloat16, out=wide[:, hq * d:hq * d + inner] if inner <= width else None,
+                                         out_scale=0.5), graph=single),
+            us_gout, nbytes=n * inner * (4 + 4 + 2 + 2), like_bytes=n * gh * gv * (4 + 2 + 2))
+    assert err.tolist()[0] == 0, err.tolist()
+    return rows
+
+
 DESIGNS = {
     "ketalix": dict(name="Ketalix", config=ketalix_config, twin=("qwen3_twin", qwen3_twin), kernels=ketalix_kernels),
     "logivik": dict(name="Logivik", config=logivik_config, twin=("ketalix_twin", ketalix_config), kernels=logivik_kernels),
+    "tarivik": dict(name="Tarivik", config=tarivik_config, twin=("ketalix_twin", ketalix_config), kernels=tarivik_kernels),
 }
 
 
@@ -1256,7 +1507,7 @@ def main() -> int:
     ap.add_argument("--sizes", default="8b", choices=["0.6b", "8b", "14b", "32b"],
                     help="layer sizes: of --workload (0.6b, 8b), or of the decode/prefill run (8b, the metric's "
                          "own, 14b, 32b)")
-    ap.add_argument("--design", default=None, choices=["ketalix", "logivik"],
+    ap.add_argument("--design", default=None, choices=["ketalix", "logivik", "tarivik"],
                     help="measure another design instead: its prefill and decode throughput beside the engine's closest "
                          "other model of equal layer sizes (Ketalix beside Qwen3, Logivik beside Ketalix), and its kernels "
                          "alone beside their like kernels (--design-sizes)")

@@ -272,6 +272,33 @@ def test_mixture_of_experts_against_the_plain_sum(dtype, n, width, ff, experts, 
     assert torch.equal(again.cpu(), got.cpu()[pick])
 
 
+@pytest.mark.parametrize("n,width,ff,experts,count,keep,top", [(70, 64, 128, 6, 3, 2, 3), (1, 72, 64, 4, 1, 1, 2),
+                                                                (700, 136, 192, 9, 3, 3, 4), (5, 256, 320, 16, 4, 2, 1)])
+def test_mixture_of_experts_on_the_tensor_cores(n, width, ff, experts, count, keep, top):
+    """bfloat16 at sizes the grouped product takes: experts with no row, with a few rows and with more rows
+    than a tile; a token's result is the same bit for bit whatever else is in the batch."""
+    from tokamak_b200.csrc import ops
+    gen = torch.Generator().manual_seed(n + width)
+    rnd = lambda *s, std=1.0: (torch.randn(*s, generator=gen) * std).to(torch.bfloat16)
+    h = rnd(n, width)
+    w = {"router": rnd(experts, width, std=0.3).float(), "correction": torch.randn(experts, generator=gen) * 0.1}
+    for e in range(experts):
+        w[f"e{e}.gate"], w[f"e{e}.up"], w[f"e{e}.down"] = rnd(ff, width, std=0.2), rnd(ff, width, std=0.2), rnd(width, ff, std=0.2)
+    m = {"router": {"experts": experts, "top": top, "groups": {"count": count, "keep": keep}}}
+    stack = lambda name: dev(torch.stack([w[f"e{e}.{name}"] for e in range(experts)]))
+    assert ops.moe_tc_takes(torch.bfloat16, width, ff)
+    gate_up, down = ops.moe_stack_gate_up(stack("gate"), stack("up")), stack("down")
+    err = torch.zeros(4, dtype=torch.int32, device="cuda")
+    route = lambda x: ops.moe_route(dev(x), dev(w["router"]), dev(w["correction"]), top=top, n_groups=count, keep=keep,
+                                    padded=True)
+    got = ops.moe_experts_tc(dev(h), route(h), gate_up, down, err)
+    close(got, _ref_moe(h, w, m), "bfloat16", scale=2.0)
+    pick = torch.randperm(n, generator=gen)[:max(1, n // 3)]
+    again = ops.moe_experts_tc(dev(h[pick]), route(h[pick]), gate_up, down, err)
+    assert torch.equal(again.cpu(), got.cpu()[pick])
+    assert err.tolist()[0] == 0
+
+
 def _attention_setup(dtype, T, H, G, d, dv, page, gen):
     """Random q, k, v of one sequence, and k, v laid into shuffled pages."""
     q = torch.randn(T, H, d, generator=gen).to(TORCH[dtype])

@@ -19,6 +19,12 @@
 // bf16(silu(gate) * up) as [tokens, n / 2]: the activation costs no pass over memory
 // (src/tokamak/model/layers.py:103).
 //
+// Grouped form (a mixture of experts): the token rows are laid out expert by expert, every expert's rows
+// padded to whole 256-row tiles, and tile_expert[tm] names the expert whose weights the row tile tm
+// multiplies (the weights are [experts * cols, k], expert e's rows from e * cols on); a negative entry is
+// a row tile that nobody uses, which every role of the pair skips.  The list is written on the device by
+// the kernel that lays the rows out, so all roles wait for the preceding kernels before they read it.
+//
 // tcgen05.commit with cluster multicast gives a stage back to both blocks; every wait on an
 // mbarrier is bounded, reports kErrWait and lets the block leave through the common exit, which
 // meets the other block at a cluster barrier before tensor memory is freed.
@@ -42,6 +48,7 @@ struct GemmPairParams {
   int rows, cols, k;
   long long ld_out;
   int mode;                 // 0: bf16 [rows, cols]; 1, 2: gated activation (silu, gelu: glu_act(mode - 1)), bf16 [rows, cols / 2]
+  const int* tile_expert;   // [ceil(rows / 256)] or null: the expert of every 256-row tile of x, negative: skipped
 };
 
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
@@ -125,8 +132,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
         const int tm = tile % n_tm, tn = tile / n_tm;
+        const int expert = p.tile_expert != nullptr ? p.tile_expert[tm] : 0;
+        if (expert < 0) continue;
         const int x_row = tm * 2 * kGpBM + (int)rank * kGpBM;
-        const int w_row = tn * kGpBN + (int)rank * kGpBNHalf;
+        const int w_row = expert * p.cols + tn * kGpBN + (int)rank * kGpBNHalf;
         for (int kb = 0; kb < n_kb; ++kb, ++it) {
           const uint32_t s = it % kGpStages, round = it / kGpStages;
           if (round > 0 && !mbar_wait(gt_smem_u32(&empty_bar[s]), (round - 1) & 1u, abort_flag)) {
@@ -152,10 +161,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       uint32_t it = 0;
       int lt = 0;
       bool ok = true;
-      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++lt) {
+      if (p.tile_expert != nullptr) pdl_wait();
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+        if (p.tile_expert != nullptr && p.tile_expert[tile % n_tm] < 0) continue;
         const int b = lt & 1, use = lt >> 1;
+        ++lt;
         if (use > 0 && !mbar_wait(gt_smem_u32(&acc_empty[b]), (uint32_t)(use - 1) & 1u, abort_flag)) {
-          set_error(p.err, kErrWait, 21, lt, b);
+          set_error(p.err, kErrWait, 21, lt - 1, b);
           *abort_flag = 1;
           break;
         }
@@ -188,12 +200,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     int lt = 0;
     bool ok = true;
-    for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++lt) {
+    if (p.tile_expert != nullptr) pdl_wait();
+    for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
       const int tm = tile % n_tm, tn = tile / n_tm;
+      if (p.tile_expert != nullptr && p.tile_expert[tm] < 0) continue;
       const int b = lt & 1, use = lt >> 1;
+      ++lt;
       ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&acc_full[b]), (uint32_t)use & 1u, abort_flag));
       if (!ok) {
-        if (lane == 0) { set_error(p.err, kErrWait, 23, lt, b); *abort_flag = 1; }
+        if (lane == 0) { set_error(p.err, kErrWait, 23, lt - 1, b); *abort_flag = 1; }
         break;
       }
       tc_fence_after();
@@ -292,8 +307,9 @@ static int make_pair_map(CUtensorMap* map, const void* ptr, long long rows, long
 // ld_w).  mode 0: out is bf16 [rows, cols]; mode 1 (cols a multiple of 128, gate and up rows of w
 // alternating in blocks of 64): out is bf16 [rows, cols / 2] = silu(gate) * up.  ld_out: elements
 // between output rows, a multiple of 8.
-TK_API int tk_gemm_bf16_pair(const void* x, const void* w, void* out, int* err, int rows, int cols, int k,
-                             long long ld_x, long long ld_w, long long ld_out, int mode, cudaStream_t stream) {
+static int gemm_bf16_pair_launch(const void* x, const void* w, void* out, int* err, int rows, int cols, int k,
+                                 long long ld_x, long long ld_w, long long ld_out, int mode, const int* tile_expert,
+                                 int experts, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (k <= 0 || k % 8 != 0 || ld_out % 8 != 0 || mode < 0 || mode > 2 || (mode != 0 && cols % 128 != 0) ||
       ((uintptr_t)out & 15u) != 0) {
@@ -302,7 +318,7 @@ TK_API int tk_gemm_bf16_pair(const void* x, const void* w, void* out, int* err, 
   CUtensorMap map_x, map_w;
   int rc = tk::make_pair_map(&map_x, x, rows, k, ld_x);
   if (rc != 0) return rc;
-  rc = tk::make_pair_map(&map_w, w, cols, k, ld_w);
+  rc = tk::make_pair_map(&map_w, w, (long long)cols * experts, k, ld_w);
   if (rc != 0) return rc;
   const size_t smem_bytes = (size_t)tk::kGpStages * tk::kGpStageBytes + 1024 /* alignment */ + 256 /* barriers */;
   static int max_pairs = 0;
@@ -328,7 +344,22 @@ TK_API int tk_gemm_bf16_pair(const void* x, const void* w, void* out, int* err, 
   const int pairs = n_tiles < max_pairs ? n_tiles : max_pairs;
   tk::GemmPairParams p;
   p.out = out; p.err = err; p.rows = rows; p.cols = cols; p.k = k; p.ld_out = ld_out; p.mode = mode;
+  p.tile_expert = tile_expert;
   // the two blocks of a pair are neighbours along x, as tcgen05's cta_group::2 wants them
   return (int)tk::launch_cluster(tk::gemm_pair_kernel, dim3(2 * pairs, 1, 1), dim3(tk::kGpThreads), smem_bytes, stream,
                                  dim3(2, 1, 1), map_x, map_w, p);
+}
+
+TK_API int tk_gemm_bf16_pair(const void* x, const void* w, void* out, int* err, int rows, int cols, int k,
+                             long long ld_x, long long ld_w, long long ld_out, int mode, cudaStream_t stream) {
+  return gemm_bf16_pair_launch(x, w, out, err, rows, cols, k, ld_x, ld_w, ld_out, mode, nullptr, 1, stream);
+}
+
+// The grouped form: x is [rows, k] with rows a multiple of 256, every 256-row tile belonging to expert
+// tile_expert[tile] (negative: skipped); w is [experts * cols, k]; out as above, row for row.
+TK_API int tk_gemm_bf16_pair_grouped(const void* x, const void* w, void* out, int* err, const int* tile_expert, int rows,
+                                     int experts, int cols, int k, long long ld_x, long long ld_w, long long ld_out,
+                                     int mode, cudaStream_t stream) {
+  if (tile_expert == nullptr || experts < 1 || rows % 256 != 0) return (int)cudaErrorInvalidValue;
+  return gemm_bf16_pair_launch(x, w, out, err, rows, cols, k, ld_x, ld_w, ld_out, mode, tile_expert, experts, stream);
 }

@@ -71,7 +71,10 @@ _SIGNATURES: dict[str, list] = {
                        _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                        c_float, c_int, _P],
     "tk_moe_tile_rows": [],
-    "tk_moe_route": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "tk_moe_pad_rows": [],
+    "tk_moe_route": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "tk_moe_gather": [_P, c_longlong, _P, _P, c_int, c_int, c_int, _P],
+    "tk_moe_combine_rows": [_P, _P, _P, _P, c_int, c_int, c_int, _P],
     "tk_moe_ffn": [_P, c_longlong, c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_moe_combine": [_P, _P, _P, c_int, c_int, c_int, _P],
     "tk_qkv_pairs": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
@@ -106,6 +109,8 @@ _SIGNATURES: dict[str, list] = {
                          _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                          c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P],
     "tk_gemm_bf16_pair": [_P, _P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, _P],
+    "tk_gemm_bf16_pair_grouped": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                                  c_int, _P],
     "tk_gemm_f32": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_sample": [_P, c_longlong, _P, _P, _P, _P, _P, _P, c_int, c_int, _P],
 }

@@ -13,6 +13,12 @@
 // one thread's sum over ascending k, so a pair's result does not depend on what else is in the batch or
 // where its row lies in a tile.  moe_combine_kernel: the weighted sum of a token's pairs in the order of
 // its choices, float32.
+//
+// For bfloat16 at sizes that the tensor-core product on pairs of SMs takes, the products run there instead
+// (gemm_pair_tcgen05.cu, grouped form): moe_sort_kernel also gives every pair a row in a layout in which
+// an expert's rows are padded to whole tiles of kMoePadRows rows and names every tile's expert;
+// moe_gather_kernel copies the tokens' rows there; gate/up with the activation in the epilogue and down
+// run over that layout, row for row; moe_combine_rows_kernel forms the weighted sum from the pairs' rows.
 #include "common.cuh"
 
 namespace tk {
@@ -21,6 +27,7 @@ constexpr int kMoeMaxExperts = 1024;
 constexpr int kMoeTileRows = 32;
 constexpr int kMoeTileCols = 64;
 constexpr int kMoeTileK = 32;
+constexpr int kMoePadRows = 256;      // the row tile of the product on pairs of SMs
 
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 #pragma unroll
@@ -103,9 +110,13 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
 
 // order: [pairs] the pairs (token * top + choice) expert by expert; tiles: [max_tiles, 3] (expert, first
 // place in order, rows) of every tile of kMoeTileRows rows; n_tiles: [1].
+// pair_row (or null): [pairs] the row of every pair in the padded layout; tile_expert: [max_pad_tiles] the
+// expert of every kMoePadRows-row tile of that layout, -1 for tiles that nobody uses.
 __global__ void moe_sort_kernel(const int* __restrict__ chosen, int* __restrict__ order, int* __restrict__ tiles,
-                                int* __restrict__ n_tiles, int pairs, int experts) {
+                                int* __restrict__ n_tiles, int pairs, int experts, int* __restrict__ pair_row,
+                                int* __restrict__ tile_expert, int max_pad_tiles) {
   __shared__ int count[kMoeMaxExperts], start[kMoeMaxExperts], cursor[kMoeMaxExperts], tile0[kMoeMaxExperts];
+  __shared__ int pad0[kMoeMaxExperts];
   pdl_trigger();
   pdl_wait();
   for (int e = threadIdx.x; e < experts; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
@@ -116,18 +127,31 @@ __global__ void moe_sort_kernel(const int* __restrict__ chosen, int* __restrict_
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int at = 0, tile = 0;
+    int at = 0, tile = 0, pad = 0;
     for (int e = 0; e < experts; ++e) {
-      start[e] = at; tile0[e] = tile;
+      start[e] = at; tile0[e] = tile; pad0[e] = pad;
       at += count[e];
       tile += (count[e] + kMoeTileRows - 1) / kMoeTileRows;
+      pad += (count[e] + kMoePadRows - 1) / kMoePadRows;
     }
     *n_tiles = tile;
   }
   __syncthreads();
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
     const int e = chosen[i];
-    if (e >= 0 && e < experts) order[start[e] + atomicAdd(&cursor[e], 1)] = i;
+    if (e >= 0 && e < experts) {
+      const int at = atomicAdd(&cursor[e], 1);
+      order[start[e] + at] = i;
+      if (pair_row != nullptr) pair_row[i] = pad0[e] * kMoePadRows + at;
+    }
+  }
+  if (tile_expert != nullptr) {
+    for (int t = threadIdx.x; t < max_pad_tiles; t += blockDim.x) tile_expert[t] = -1;
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+      const int n = (count[e] + kMoePadRows - 1) / kMoePadRows;
+      for (int i = 0; i < n && pad0[e] + i < max_pad_tiles; ++i) tile_expert[pad0[e] + i] = e;
+    }
   }
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     const int n = (count[e] + kMoeTileRows - 1) / kMoeTileRows;
@@ -223,13 +247,46 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
   out[idx] = acc;
 }
 
+// rows[pair_row[pair]] = h[pair / top], 16 bytes a thread (width a multiple of 8 bfloat16).
+__global__ void moe_gather_kernel(const uint4* __restrict__ h, long long h_stride16, uint4* __restrict__ rows,
+                                  const int* __restrict__ pair_row, int pairs, int top, int width16) {
+  pdl_trigger();
+  pdl_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)pairs * width16) return;
+  const int pair = (int)(idx / width16), c = (int)(idx - (long long)pair * width16);
+  rows[(size_t)pair_row[pair] * width16 + c] = h[(size_t)(pair / top) * h_stride16 + c];
+}
+
+// out[t] = sum over the token's choices of weight * y[row of the pair], float32, in the order of the choices.
+__global__ void moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ weights,
+                                        const int* __restrict__ pair_row, float* __restrict__ out, int n_tokens,
+                                        int width, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int w2 = width >> 1;
+  if (idx >= (long long)n_tokens * w2) return;
+  const int t = (int)(idx / w2), c = (int)(idx - (long long)t * w2);
+  float a0 = 0.0f, a1 = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    const float w = weights[(size_t)t * top + k];
+    const float2 v = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(y + (size_t)pair_row[(size_t)t * top + k] * width)[c]);
+    a0 += w * v.x; a1 += w * v.y;
+  }
+  reinterpret_cast<float2*>(out + (size_t)t * width)[c] = make_float2(a0, a1);
+}
+
 }  // namespace tk
 
 TK_API int tk_moe_tile_rows() { return tk::kMoeTileRows; }
 
+TK_API int tk_moe_pad_rows() { return tk::kMoePadRows; }
+
 TK_API int tk_moe_route(const void* h, const float* router, const float* correction, int* chosen, float* weights,
-                        int* order, int* tiles, int* n_tiles, int n_tokens, int width, int experts, int n_groups,
-                        int keep, int top, int dtype, cudaStream_t stream) {
+                        int* order, int* tiles, int* n_tiles, int* pair_row, int* tile_expert, int max_pad_tiles,
+                        int n_tokens, int width, int experts, int n_groups, int keep, int top, int dtype,
+                        cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (experts < 1 || experts > tk::kMoeMaxExperts || n_groups < 1 || experts % n_groups || keep < 1 || keep > n_groups ||
       top < 1 || top > keep * (experts / n_groups)) {
@@ -243,8 +300,28 @@ TK_API int tk_moe_route(const void* h, const float* router, const float* correct
                                              weights, n_tokens, width, experts, n_groups, keep, top));
   if (e != cudaSuccess) return (int)e;
   e = tk::launch(tk::moe_sort_kernel, dim3(1), dim3(1024), 0, stream, (const int*)chosen, order, tiles, n_tiles,
-                 n_tokens * top, experts);
+                 n_tokens * top, experts, pair_row, tile_expert, max_pad_tiles);
   return (int)e;
+}
+
+TK_API int tk_moe_gather(const void* h, long long h_stride, void* rows, const int* pair_row, int n_tokens, int top,
+                         int width, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (width % 8 != 0 || h_stride % 8 != 0 || ((uintptr_t)h & 15u) != 0 || ((uintptr_t)rows & 15u) != 0) {
+    return (int)cudaErrorInvalidValue;
+  }
+  const long long total = (long long)n_tokens * top * (width / 8);
+  return (int)tk::launch(tk::moe_gather_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                         (const uint4*)h, h_stride / 8, (uint4*)rows, pair_row, n_tokens * top, top, width / 8);
+}
+
+TK_API int tk_moe_combine_rows(const void* y, const float* weights, const int* pair_row, float* out, int n_tokens,
+                               int width, int top, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (width % 2 != 0) return (int)cudaErrorInvalidValue;
+  const long long total = (long long)n_tokens * (width / 2);
+  return (int)tk::launch(tk::moe_combine_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                         (const __nv_bfloat16*)y, weights, pair_row, out, n_tokens, width, top);
 }
 
 // gated != 0: out[pair] = act(a[pair / a_div] b0^T) * (a[pair / a_div] b1^T) in the activation type;

@@ -833,15 +833,22 @@ def moe_tile_rows() -> int:
 
 class MoeRouting:
     """What :func:`moe_route` leaves on the device: ``chosen`` / ``weights`` ``[tokens, top]``, the pairs
-    ``token * top + choice`` laid out expert by expert (``order``), and the products' row tiles."""
+    ``token * top + choice`` laid out expert by expert (``order``), and the products' row tiles.  With
+    ``padded``: also every pair's row in the layout whose experts start on whole tiles of
+    :func:`moe_pad_rows` rows (``pair_row``) and every such tile's expert (``tile_expert``, -1: unused)."""
 
-    def __init__(self, chosen, weights, order, tiles, n_tiles, max_tiles):
+    def __init__(self, chosen, weights, order, tiles, n_tiles, max_tiles, pair_row=None, tile_expert=None):
         self.chosen, self.weights, self.order, self.tiles, self.n_tiles, self.max_tiles = (
             chosen, weights, order, tiles, n_tiles, max_tiles)
+        self.pair_row, self.tile_expert = pair_row, tile_expert
+
+
+def moe_pad_rows() -> int:
+    return _lib().tk_moe_pad_rows()
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, *, top: int, n_groups: int,
-              keep: int) -> MoeRouting:
+              keep: int, padded: bool = False) -> MoeRouting:
     """Scores ``sigmoid(h router^T)`` in float32, choice by score plus ``correction`` among the ``keep`` groups
     of neighbouring experts whose two best choice scores add up highest, weights the plain scores."""
     _want(h, None, "h"); _want(router, torch.float32, "router")
@@ -859,10 +866,67 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | 
     order = torch.empty(pairs, dtype=torch.int32, device=dev)
     tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=dev)
     n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    pair_row = tile_expert = None
+    if padded:
+        pair_row = torch.empty(pairs, dtype=torch.int32, device=dev)
+        tile_expert = torch.empty(min(pairs, pairs // moe_pad_rows() + experts), dtype=torch.int32, device=dev)
     _check(_lib().tk_moe_route(h.data_ptr(), router.data_ptr(), _ptr(correction), chosen.data_ptr(), weights.data_ptr(),
-                                  order.data_ptr(), tiles.data_ptr(), n_tiles.data_ptr(), n, width, experts, n_groups,
+                                  order.data_ptr(), tiles.data_ptr(), n_tiles.data_ptr(), _ptr(pair_row), _ptr(tile_expert),
+                                  tile_expert.numel() if padded else 0, n, width, experts, n_groups,
                                   keep, top, dtype_code(h.dtype), _stream()), "moe_route")
-    return MoeRouting(chosen, weights, order, tiles, n_tiles, max_tiles)
+    return MoeRouting(chosen, weights, order, tiles, n_tiles, max_tiles, pair_row, tile_expert)
+
+
+def moe_tc_takes(dtype: torch.dtype, width: int, ff: int) -> bool:
+    """Whether :func:`moe_experts_tc` runs these sizes: bfloat16, an inner size in whole blocks of the fused
+    activation, rows that TMA and 16-byte stores can address."""
+    return dtype == torch.bfloat16 and ff % SWIGLU_TILE_BLOCK == 0 and width % 8 == 0 and PAIR_GEMM_POLICY != "off"
+
+
+def moe_stack_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """``[experts, 2 ff, width]`` with every expert's gate and up rows alternating in blocks of
+    ``SWIGLU_TILE_BLOCK``, as the fused activation of the product wants them."""
+    experts, ff, width = w_gate.shape
+    b = SWIGLU_TILE_BLOCK
+    return torch.stack([w_gate.view(experts, ff // b, b, width), w_up.view(experts, ff // b, b, width)],
+                       dim=2).reshape(experts, 2 * ff, width).contiguous()
+
+
+def moe_experts_tc(h: torch.Tensor, routing: MoeRouting, w_gate_up: torch.Tensor, w_down: torch.Tensor, err: torch.Tensor,
+                   activation: str = "silu") -> torch.Tensor:
+    """:func:`moe_experts` on the tensor cores (bfloat16): the tokens' rows are copied into the padded layout
+    of ``routing``, the grouped product on pairs of SMs forms ``act(gate) * up`` in its epilogue and then the
+    down product, row for row, and the weighted sum reads the pairs' rows.  ``w_gate_up`` is what
+    :func:`moe_stack_gate_up` returns, ``w_down`` ``[experts, width, ff]``.  float32 ``[tokens, width]``."""
+    _want(h, torch.bfloat16, "h"); _want(w_gate_up, torch.bfloat16, "w_gate_up"); _want(w_down, torch.bfloat16, "w_down")
+    n, width = h.shape
+    experts, ff2, _ = w_gate_up.shape
+    ff = ff2 // 2
+    top = routing.chosen.shape[1]
+    if routing.pair_row is None or w_gate_up.shape != (experts, 2 * ff, width) or w_down.shape != (experts, width, ff):
+        raise KernelError("moe_experts_tc: the routing must be padded and the weights stacked for these sizes")
+    if not moe_tc_takes(h.dtype, width, ff) or h.stride(1) != 1 or h.stride(0) % 8:
+        raise KernelError("moe_experts_tc does not take these sizes")
+    if activation not in GLU_ACTIVATIONS:
+        raise KernelError(f"unknown activation {activation!r}")
+    flush_chains()
+    lib, r = _lib(), routing
+    rows = r.tile_expert.numel() * moe_pad_rows()
+    xs = torch.empty((rows, width), dtype=torch.bfloat16, device=h.device)
+    act = torch.empty((rows, ff), dtype=torch.bfloat16, device=h.device)
+    y = torch.empty((rows, width), dtype=torch.bfloat16, device=h.device)
+    out = torch.empty((n, width), dtype=torch.float32, device=h.device)
+    _check(lib.tk_moe_gather(h.data_ptr(), h.stride(0), xs.data_ptr(), r.pair_row.data_ptr(), n, top, width, _stream()),
+           "moe_gather")
+    _check(lib.tk_gemm_bf16_pair_grouped(xs.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), err.data_ptr(),
+                                         r.tile_expert.data_ptr(), rows, experts, 2 * ff, width, width, width, ff,
+                                         1 + GLU_ACTIVATIONS[activation], _stream()), "gemm_pair_grouped (gate, up)")
+    _check(lib.tk_gemm_bf16_pair_grouped(act.data_ptr(), w_down.data_ptr(), y.data_ptr(), err.data_ptr(),
+                                         r.tile_expert.data_ptr(), rows, experts, width, ff, ff, ff, width, 0, _stream()),
+           "gemm_pair_grouped (down)")
+    _check(lib.tk_moe_combine_rows(y.data_ptr(), r.weights.data_ptr(), r.pair_row.data_ptr(), out.data_ptr(), n, width,
+                                   top, _stream()), "moe_combine_rows")
+    return out
 
 
 def moe_experts(h: torch.Tensor, routing: MoeRouting, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,

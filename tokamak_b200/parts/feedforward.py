@@ -157,6 +157,12 @@ class MixtureOfExperts:
         stack = lambda name: torch.stack([tensors[prefix + spec.expert_prefix.format(e) + name]
                                           for e in range(spec.num_experts)]).contiguous()
         self.w_gate, self.w_up, self.w_down = stack(spec.gate_name), stack(spec.up_name), stack(spec.down_name)
+        # bfloat16 at sizes the product on pairs of SMs takes: gate and up rows alternate in blocks, so that
+        # the activation is the product's epilogue; the two matrices are then kept only in that form
+        self.w_gate_up = None
+        if ops.moe_tc_takes(self.w_gate.dtype, spec.hidden_size, spec.intermediate_size):
+            self.w_gate_up = ops.moe_stack_gate_up(self.w_gate, self.w_up)
+            self.w_gate = self.w_up = None
 
     @staticmethod
     def expected_tensors(spec: MoESpec, prefix: str) -> dict[str, TensorReq]:
@@ -174,14 +180,18 @@ class MixtureOfExperts:
 
     def weight_bytes(self) -> int:
         """What a step of one token reads: the router and ``top`` experts (a large step reads all)."""
-        per_expert = tensor_bytes(self.w_gate, self.w_up, self.w_down) // self.spec.num_experts
+        per_expert = tensor_bytes(self.w_gate, self.w_up, self.w_gate_up, self.w_down) // self.spec.num_experts
         return tensor_bytes(self.router, self.correction) + self.spec.top * per_expert
 
     def forward(self, h, step):
         spec = self.spec
         if isinstance(h, OwedNorm):
             h = h.materialize()
+        tc = self.w_gate_up is not None
         routing = ops.moe_route(h, self.router, self.correction, top=spec.top, n_groups=spec.num_groups,
-                                keep=spec.keep_groups)
-        out = ops.moe_experts(h, routing, self.w_gate, self.w_up, self.w_down, activation=spec.activation)
+                                keep=spec.keep_groups, padded=tc)
+        if tc:
+            out = ops.moe_experts_tc(h, routing, self.w_gate_up, self.w_down, step.err, activation=spec.activation)
+        else:
+            out = ops.moe_experts(h, routing, self.w_gate, self.w_up, self.w_down, activation=spec.activation)
         return out.unsqueeze(0)         # float32 sums, one part: the consuming norm reads them as they are
