@@ -1202,7 +1202,12 @@ def tarivik_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
 
     def step_of(n, n_req, start):
         per = n // n_req
+        none = i32([])
+        rec, n_parts, n_split = ops.prefill_tc_records([r * per for r in range(n_req)], [per] * n_req, [start + per] * n_req,
+                                                       list(range(n_req)), heads=s["heads"], sms=ops.sm_count(torch.device(dev, 0)))
         return SimpleNamespace(
+            decode_items=i32(list(range(n))) if per == 1 else none, prefill_items=none if per == 1 else i32(list(range(n))),
+            prefill_tiles=none, prefill_tc=ops.PrefillItems(torch.from_numpy(rec).to(dev), n_parts, n_split),
             positions=i32([start + i for _ in range(n_req) for i in range(per)]),
             tok_req=i32([r for r in range(n_req) for _ in range(per)]), req_q_start=i32([r * per for r in range(n_req)]),
             req_q_len=i32([per] * n_req), req_kv_len=i32([start + per] * n_req), req_slot=i32(list(range(n_req))),

@@ -359,6 +359,92 @@ def test_chunked_attention_with_keys_that_stand_out(dtype, chunk, page):
     assert err.tolist()[0] == 0
 
 
+def _tiled_step(q_lens, slots, starts, heads):
+    """:func:`fake_step` with what the attention mixer's choice of kernels reads besides."""
+    from tokamak_b200.csrc import ops
+    step = fake_step(q_lens, slots, starts)
+    q_start = step.req_q_start.tolist()
+    kv_len = [s + n for s, n in zip(starts, q_lens)]
+    rec, n_parts, n_split = ops.prefill_tc_records(q_start, q_lens, kv_len, slots, heads=heads,
+                                                   sms=ops.sm_count(torch.device("cuda", 0)))
+    step.prefill_tc = ops.PrefillItems(torch.from_numpy(rec).cuda(), n_parts, n_split)
+    step.decode_items = i32([q_start[r] for r, n in enumerate(q_lens) if n == 1])
+    step.prefill_items = i32([q_start[r] + j for r, n in enumerate(q_lens) if n > 1 for j in range(n)])
+    step.prefill_tiles = i32([])
+    step.max_kv_len = max(kv_len)
+    return step
+
+
+@pytest.mark.parametrize("chunk", [24, 64, 100, 256, 1000])
+@pytest.mark.parametrize("H,G,d", [(8, 2, 64), (4, 4, 128), (6, 1, 128)])
+def test_chunked_attention_on_the_tiled_kernels(chunk, H, G, d):
+    """bfloat16 heads of 64 and 128 channels go to the tensor-core kernels, which know the chunks, the distance
+    bias and the sinks too: a prompt's portion that crosses chunks and blocks of 256 rows, single tokens at the
+    chunks' edges (equal splits and tiles dealt out), and both kinds in one step, with keys that stand out just
+    inside and just outside every probe's chunk."""
+    from tokamak_b200.csrc import ops
+    from tokamak_b200.cache.device import KVView
+    from tokamak_b200.parts.attention import paged_attention
+    gen = torch.Generator().manual_seed(chunk * 10 + H)
+    T, page = 700, 16
+    q, k, v = _attention_setup("bfloat16", T, H, G, d, d, page, gen)
+    probes = sorted({min(T - 1, max(0, i)) for c in range(0, T + chunk, chunk) for i in (c - 1, c, c + 1)} | {T - 1, 0})
+    probes = probes[:6] + probes[-12:] if len(probes) > 18 else probes
+    for i in probes:
+        first = i - i % chunk
+        q[i] *= 3.0
+        if first != i:
+            k[first] = (q[i, ::H // G].float() * 0.5).to(k.dtype)
+        if first > 0 and (first - 1) not in probes:
+            k[first - 1] = (q[i, ::H // G].float() * 2.0).to(k.dtype)
+    sinks = torch.randn(H, generator=gen)
+    slopes = plain.head_slopes(H).float()
+    want = plain.chunked_attention(q.double(), k.double(), v.double(), 0.3, chunk, sinks.double())
+    n_pages = -(-T // page) + 7
+    ids = torch.randperm(n_pages, generator=gen)[:-(-T // page)]
+    kc = torch.full((n_pages, G, page, d), float("nan"), dtype=torch.bfloat16)
+    vc = torch.full((n_pages, G, page, d), float("nan"), dtype=torch.bfloat16)
+    kc[ids[-1]] = 0.0                            # the rest of a request's last page is cleared by the kernel that writes it
+    vc[ids[-1]] = 0.0
+    for p in range(T):
+        kc[ids[p // page], :, p % page] = k[p]
+        vc[ids[p // page], :, p % page] = v[p]
+    table = torch.full((3, 64), -1, dtype=torch.int32)
+    table[1, :len(ids)] = ids.int()
+    view = KVView(dev(kc), dev(vc), dev(table), page, None)
+    kw = dict(scale=0.3, window=None, sinks=dev(sinks), chunk=chunk, slopes=dev(slopes))
+
+    def run(q_lens, starts):
+        step = _tiled_step(q_lens, [1] * len(q_lens), starts, H)
+        rows = torch.cat([q[s:s + n] for n, s in zip(q_lens, starts)])
+        out = torch.full((len(rows), H, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+        paged_attention(dev(rows), out, view, step, **kw)
+        torch.cuda.synchronize()
+        assert step.err.tolist()[0] == 0
+        close(out, torch.cat([want[s:s + n] for n, s in zip(q_lens, starts)]), "bfloat16", scale=4.0)
+        return step
+
+    assert ops.decode_kernel_takes(H, G, d, page) and ops.prefill_tc_kernel_takes(H, G, d, page)
+    run([T], [0])                                # the whole prompt
+    run([T - 130], [130])                        # a portion that begins inside a chunk, a page and a key tile
+    run([1] * len(probes), probes)               # single tokens
+    run([1, T - 333, 1, 1], [probes[-2], 333, probes[1], probes[len(probes) // 2]])      # both kinds in one step
+    # the two decode kernels by name, with few and many splits
+    step = _tiled_step([1] * len(probes), [1] * len(probes), probes, H)
+    rows = dev(torch.cat([q[i:i + 1] for i in probes]))
+    ref = torch.cat([want[i:i + 1] for i in probes])
+    args = (view.k, view.v, step.decode_items, step.positions, step.tok_req, step.req_slot, view.table, step.err)
+    for n_splits in (1, 3, 16):
+        out = torch.full_like(rows, float("nan"))
+        ops.attention_decode(rows, out, *args, n_splits=n_splits, **kw)
+        close(out, ref, "bfloat16", scale=4.0)
+    for blocks in (1, 5, 64):
+        out = torch.full_like(rows, float("nan"))
+        ops.attention_decode_balanced(rows, out, *args, blocks=blocks, **kw)
+        close(out, ref, "bfloat16", scale=4.0)
+    assert step.err.tolist()[0] == 0
+
+
 def _mixer_part(kind, spec, weights, dtype):
     from tokamak_b200.parts.base import MIXERS, Runtime
     rt = Runtime(device=torch.device("cuda"), dtype=TORCH[dtype])
@@ -431,6 +517,29 @@ def test_mlstm_mixer_alone_with_memory_normaliser_and_maximum_carried(dtype, hea
     view = _state_views(part)
     seqs = [torch.randn(sum(c), width, generator=gen).to(TORCH[dtype]) for c in CUTS]
     got = run_in_steps(seqs, SLOTS, CUTS, lambda rows, step: torch.as_tensor(
+        part.forward(dev(rows), step, view)).float().reshape(-1, rows.shape[0], width).sum(0))
+    m = {"heads": heads, "dim": dk, "vdim": dv, "gate_cap": cap}
+    for g, x in zip(got, seqs):
+        close(g, plain.mlstm_mixer(x.double(), {k: v.double() for k, v in w.items()}, m, 1e-6), dtype, scale=3.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mlstm_running_maximum_over_long_portions(dtype):
+    """Portions longer than one stretch of the gates' scan, ending inside a stretch and inside a lane's share
+    of it, beside a single token; the maximum rises in one head and stays at its start in another."""
+    from tokamak_b200.parts.mlstm import MlstmSpec
+    gen = torch.Generator().manual_seed(77)
+    width, heads, dk, dv, cap = 32, 2, 16, 24, 8.0
+    w = _random_weights({"q": ((heads * dk, width), 0.4, 0), "k": ((heads * dk, width), 0.4, 0), "v": ((heads * dv, width), 0.3, 0),
+                         "g": ((heads * dv, width), 0.3, 0), "o": ((width, heads * dv), 0.2, 0), "norm": ((heads * dv,), 0.2, 1.0),
+                         "i": ((heads, width), 0.6, 0), "i.b": ((heads,), 0.0, 0.0), "f": ((heads, width), 0.6, 0),
+                         "f.b": ((heads,), 0.0, 3.0)}, gen, dtype)
+    w["i.b"] = torch.tensor([3.0, -9.0])
+    part = _mixer_part("mlstm", MlstmSpec(width, heads, dk, dv, cap, 1e-6), w, dtype)
+    view = _state_views(part)
+    cuts = [[150, 1, 137, 1, 2], [1, 301, 0, 130, 1]]
+    seqs = [torch.randn(sum(c), width, generator=gen).to(TORCH[dtype]) for c in cuts]
+    got = run_in_steps(seqs, [3, 0], cuts, lambda rows, step: torch.as_tensor(
         part.forward(dev(rows), step, view)).float().reshape(-1, rows.shape[0], width).sum(0))
     m = {"heads": heads, "dim": dk, "vdim": dv, "gate_cap": cap}
     for g, x in zip(got, seqs):

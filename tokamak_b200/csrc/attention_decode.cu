@@ -52,6 +52,8 @@ struct DecodeParams {
   float scale_log2;             // softmax scale * log2(e)
   float cap_log2, inv_cap;      // score cap * log2(e) (0: none) and scale / cap
   const float* sinks;           // [n_q_heads] or null: a term of every softmax denominator
+  int chunk;                    // > 0: a token sees only the keys of its own block of that many positions
+  const float* slopes;          // [n_q_heads] or null: a key n positions back loses slope * n of its score
 };
 
 template <int D, int STAGES>
@@ -74,7 +76,13 @@ attn_decode_split_kernel(DecodeParams p) {
   bool bad = (pos < 0 || r < 0 || r >= p.n_reqs);
   if (bad && threadIdx.x == 0) set_error(p.err, pos < 0 ? kErrPosition : kErrRequest, tok, pos, r);
   const int* table = p.block_table + (size_t)(bad ? 0 : p.req_slot[r]) * p.max_pages;
-  const int lo = (!bad && p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+  const int lo = bad ? 0 : first_visible(pos, p.window, p.chunk);
+  // distance slopes of this thread's two rows (query heads hkv * group + g and + g + 8), in units of log2
+  float slope2[2] = {0.0f, 0.0f};
+  if (p.slopes != nullptr) {
+    if (g < group) slope2[0] = p.slopes[hkv * group + g] * 1.4426950408889634f;
+    if (g + 8 < group) slope2[1] = p.slopes[hkv * group + g + 8] * 1.4426950408889634f;
+  }
 
   // key tiles of this block
   const int first_tile = lo / kDecTile;
@@ -191,7 +199,8 @@ attn_decode_split_kernel(DecodeParams p) {
       for (int e = 0; e < 4; ++e) {
         const int key = tile * kDecTile + nt * 8 + 2 * t4 + (e & 1);
         const bool valid = key >= lo && key <= pos;
-        s[nt][e] = valid ? capped_score_log2(s[nt][e], p.scale_log2, p.cap_log2, p.inv_cap) : -INFINITY;
+        s[nt][e] = valid ? capped_score_log2(s[nt][e], p.scale_log2, p.cap_log2, p.inv_cap) - slope2[e >> 1] * (float)(pos - key)
+                         : -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
       }
     }
@@ -411,6 +420,8 @@ struct DecodeBalParams {
   float scale_log2;
   float cap_log2, inv_cap;      // as in DecodeParams
   const float* sinks;
+  int chunk;                    // as in DecodeParams
+  const float* slopes;
 };
 
 // The block that holds tile t of the sequence of T tiles: the largest c with T c / G <= t.
@@ -446,7 +457,7 @@ attn_decode_balanced_kernel(DecodeBalParams p) {
     if (pos < 0 || r < 0 || r >= p.n_reqs) {
       set_error(p.err, pos < 0 ? kErrPosition : kErrRequest, tok, pos, r);
     } else {
-      const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+      const int lo = first_visible(pos, p.window, p.chunk);
       tiles = pos / kDecTile - lo / kDecTile + 1;
     }
     s_first[i + 1] = tiles;
@@ -502,7 +513,13 @@ attn_decode_balanced_kernel(DecodeBalParams p) {
     const int pos = p.positions[tok];
     const int r = p.tok_req[tok];
     const int* table = p.block_table + (size_t)p.req_slot[r] * p.max_pages;
-    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int lo = first_visible(pos, p.window, p.chunk);
+    // distance slopes of this thread's two rows (query heads hkv * group + g and + g + 8), in units of log2
+    float slope2[2] = {0.0f, 0.0f};
+    if (p.slopes != nullptr) {
+      if (g < group) slope2[0] = p.slopes[hkv * group + g] * 1.4426950408889634f;
+      if (g + 8 < group) slope2[1] = p.slopes[hkv * group + g + 8] * 1.4426950408889634f;
+    }
     const int first_tile = lo / kDecTile;
     const int last_tile = pos / kDecTile;
     const int my_begin = first_tile + tile0;
@@ -602,7 +619,8 @@ attn_decode_balanced_kernel(DecodeBalParams p) {
         for (int e = 0; e < 4; ++e) {
           const int key = tile * kDecTile + nt * 8 + 2 * t4 + (e & 1);
           const bool valid = key >= lo && key <= pos;
-          s[nt][e] = valid ? capped_score_log2(s[nt][e], p.scale_log2, p.cap_log2, p.inv_cap) : -INFINITY;
+          s[nt][e] = valid ? capped_score_log2(s[nt][e], p.scale_log2, p.cap_log2, p.inv_cap) - slope2[e >> 1] * (float)(pos - key)
+                           : -INFINITY;
           mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
         }
       }
@@ -843,7 +861,7 @@ TK_API int tk_attention_decode(const void* q, void* out, const void* k_cache, co
                                int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
                                int head_dim, int page_size, int max_pages, int num_pages, int window,
                                int n_splits, float scale, float softcap, const float* sinks,
-                               cudaStream_t stream) {
+                               int chunk, const float* slopes, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   const int group = n_kv_heads > 0 ? n_q_heads / n_kv_heads : 0;
   if (n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || group > 16 || page_size % 16 != 0 ||
@@ -866,7 +884,7 @@ TK_API int tk_attention_decode(const void* q, void* out, const void* k_cache, co
   p.scale_log2 = scale * 1.4426950408889634f;
   p.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
   p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
-  p.sinks = sinks;
+  p.sinks = sinks; p.chunk = chunk; p.slopes = slopes;
   if (head_dim == 128) return tk::launch_decode<128>(p, stream);
   return tk::launch_decode<64>(p, stream);
 }
@@ -884,7 +902,7 @@ TK_API int tk_attention_decode_balanced(const void* q, void* out, const void* k_
                                         int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
                                         int head_dim, int page_size, int max_pages, int num_pages, int window,
                                         int blocks, float scale, float softcap, const float* sinks,
-                                        cudaStream_t stream) {
+                                        int chunk, const float* slopes, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   const int group = n_kv_heads > 0 ? n_q_heads / n_kv_heads : 0;
   if (n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || group > 16 || page_size % 16 != 0 || blocks < 1 ||
@@ -901,7 +919,7 @@ TK_API int tk_attention_decode_balanced(const void* q, void* out, const void* k_
   p.scale_log2 = scale * 1.4426950408889634f;
   p.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
   p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
-  p.sinks = sinks;
+  p.sinks = sinks; p.chunk = chunk; p.slopes = slopes;
   if (head_dim == 128) return tk::launch_decode_balanced<128>(p, blocks, stream);
   return tk::launch_decode_balanced<64>(p, blocks, stream);
 }

@@ -82,6 +82,8 @@ struct AttnTcParams {
   float scale_log2;
   float cap_log2, inv_cap;       // score cap * log2(e) (0: none) and scale / cap
   const float* sinks;            // [n_q_heads] or null: a term of every softmax denominator
+  int chunk;                     // > 0: a token sees only the keys of its own block of that many positions
+  const float* slopes;           // [n_q_heads] or null: a key n positions back loses slope * n of its score
 };
 
 struct AttnItem {        // what a block's roles need of an item
@@ -133,18 +135,18 @@ __device__ __forceinline__ void group_sync(int t) {
 
 // The range of key tiles that query tile t visits within an item; empty when last < first.
 struct TileRange { int rows, pos0, first, last; };
-__device__ __forceinline__ TileRange tile_range(const AttnItem& it, int t, int window) {
+__device__ __forceinline__ TileRange tile_range(const AttnItem& it, int t, int window, int chunk) {
   TileRange g;
   g.rows = min(kAtBM, it.rows - t * kAtBM);
   g.pos0 = it.pos0 + t * kAtBM;
-  const int lo = (window > 0 && g.pos0 - window + 1 > 0) ? g.pos0 - window + 1 : 0;
+  const int lo = first_visible(g.pos0, window, chunk);
   g.first = max(lo / kAtBN, it.kt_begin);
   g.last = g.rows > 0 ? min((g.pos0 + g.rows - 1) / kAtBN, it.kt_end - 1) : g.first - 1;
   return g;
 }
-// First key tile that the item loads at all (tile 0 has the lowest window edge).
-__device__ __forceinline__ int item_first_kt(const AttnItem& it, int window) {
-  const int lo = (window > 0 && it.pos0 - window + 1 > 0) ? it.pos0 - window + 1 : 0;
+// First key tile that the item loads at all (its first row has the lowest edge of window and chunk).
+__device__ __forceinline__ int item_first_kt(const AttnItem& it, int window, int chunk) {
+  const int lo = first_visible(it.pos0, window, chunk);
   return max(lo / kAtBN, it.kt_begin);
 }
 
@@ -305,9 +307,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     struct Walk { int first_kt, n_kt, lo_block, pos_last, hkv; const int* table; };
     auto walk_of = [&](const AttnItem& it) {
       Walk g;
-      g.first_kt = item_first_kt(it, p.window);
+      g.first_kt = item_first_kt(it, p.window, p.chunk);
       g.n_kt = it.valid ? max(0, it.kt_end - g.first_kt) : 0;
-      g.lo_block = (p.window > 0 && it.pos0 - p.window + 1 > 0) ? it.pos0 - p.window + 1 : 0;
+      g.lo_block = first_visible(it.pos0, p.window, p.chunk);
       g.pos_last = it.pos0 + it.rows - 1;
       g.hkv = it.head / group;
       g.table = p.block_table + (size_t)it.slot * p.max_pages;
@@ -473,8 +475,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               if (!it.valid) {
                 ended = true;
               } else {
-                my = tile_range(it, t, p.window);
-                first_kt = item_first_kt(it, p.window);
+                my = tile_range(it, t, p.window, p.chunk);
+                first_kt = item_first_kt(it, p.window, p.chunk);
                 n_kt = max(0, it.kt_end - first_kt);
                 j = 0;
                 par = s;
@@ -557,11 +559,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive(gt_smem_u32(&work_empty[s]));
       if (!it.valid) break;
-      const TileRange my = tile_range(it, t, p.window);
+      const TileRange my = tile_range(it, t, p.window, p.chunk);
       if (my.rows <= 0) continue;                       // the item has one query tile only
       const bool row_valid = row < my.rows;
       const int pos_r = my.pos0 + row;
-      const int lo_r = (p.window > 0 && pos_r - p.window + 1 > 0) ? pos_r - p.window + 1 : 0;
+      const int lo_r = first_visible(pos_r, p.window, p.chunk);
+      const float slope_l2 = p.slopes != nullptr ? p.slopes[it.head] * 1.4426950408889634f : 0.0f;
       const int my_kt = my.last - my.first + 1;         // <= 0: a part without keys for this tile
       float m_ref = -INFINITY, l_sum = 0.0f;
       if (row == 0) tl_value(30, 10 + t, (unsigned)it.index);
@@ -613,9 +616,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         // With a cap the scores are bounded here, cap * tanh(scale * s / cap), and are in units of
         // log2 from then on (tanh is monotonic: the maximum is the bounded raw maximum).
+        // A distance bias does the same, and the maximum is then that of the biased scores.
         const bool capped = p.cap_log2 != 0.0f;
-        const float eff_scale = capped ? 1.0f : p.scale_log2;
-        if (capped) {
+        const bool biased = slope_l2 != 0.0f;
+        const float eff_scale = (capped || biased) ? 1.0f : p.scale_log2;
+        if (biased) {
+          mx = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < kAtBN; ++c) {
+            if (sv[c] != -INFINITY) {
+              sv[c] = capped_score_log2(sv[c], p.scale_log2, p.cap_log2, p.inv_cap) - slope_l2 * (float)(pos_r - (key_first + c));
+            }
+            mx = fmaxf(mx, sv[c]);
+          }
+        } else if (capped) {
 #pragma unroll
           for (int c = 0; c < kAtBN; ++c) {
             if (sv[c] != -INFINITY) sv[c] = capped_score_log2(sv[c], p.scale_log2, p.cap_log2, p.inv_cap);
@@ -931,7 +945,7 @@ TK_API int tk_attention_prefill_tc(const void* q, void* out, const void* k_cache
                                    float* part_o, float* part_ml, int* part_count, int n_tokens, int n_records,
                                    int n_q_heads, int n_kv_heads, int head_dim, int page_size, int max_pages,
                                    int num_pages, int window, float scale, float softcap, const float* sinks,
-                                   cudaStream_t stream) {
+                                   int chunk, const float* slopes, cudaStream_t stream) {
   if (n_records <= 0) return 0;
   if (!tk_attention_prefill_tc_takes(n_q_heads, n_kv_heads, head_dim, page_size) || n_q_heads > 65535 ||
       (long long)n_records * n_q_heads > 0x3fffffffLL) {
@@ -974,7 +988,7 @@ TK_API int tk_attention_prefill_tc(const void* q, void* out, const void* k_cache
   p.scale_log2 = scale * 1.4426950408889634f;
   p.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
   p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
-  p.sinks = sinks;
+  p.sinks = sinks; p.chunk = chunk; p.slopes = slopes;
   const long long n_items = (long long)n_records * n_q_heads;
   const int blocks = (int)(n_items < sms[dev] ? n_items : sms[dev]);
   if (head_dim == 128) return tk::launch_prefill_tc<128>(mq, mk, mv, p, blocks, stream);

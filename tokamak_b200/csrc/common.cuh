@@ -95,6 +95,14 @@ __device__ __forceinline__ float capped_score_log2(float dot, float scale_log2, 
   return cap_log2 * (1.0f - __fdividef(2.0f, t + 1.0f));
 }
 
+// The first position that a query at `pos` sees: the edge of its window (window > 0) or the start of its
+// block of `chunk` positions (chunk > 0), whichever is later.  It never falls as `pos` grows.
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+  int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (chunk > 0) lo = max(lo, pos - pos % chunk);
+  return lo;
+}
+
 // What a sink adds to a softmax denominator whose terms are 2^(score_log2 - m): 2^(sink log2(e) - m).
 __device__ __forceinline__ float sink_term_log2(const float* sinks, int head, float m) {
   return sinks != nullptr ? exp2f(sinks[head] * 1.4426950408889634f - m) : 0.0f;

@@ -6,8 +6,8 @@
 //   experts of the `keep` best groups can be chosen; the `top` experts with the largest c are chosen
 //   out = sum over the chosen e of s_e * W_down,e (act(W_gate,e h) * (W_up,e h))
 //
-// Five kernels.  moe_route_kernel: a warp per token forms the logits and makes the choice (ties go to the
-// lower index).  moe_sort_kernel: one block counts the (token, choice) pairs of every expert, lays the
+// Five kernels.  moe_route_kernel: a block per token forms the logits, and its first warp makes the choice
+// (ties go to the lower index).  moe_sort_kernel: one block counts the (token, choice) pairs of every expert, lays the
 // pairs out expert by expert and lists the row tiles of the products.  moe_ffn_kernel: the experts'
 // products over those tiles, first gate and up with the activation, then down; an output element is
 // one thread's sum over ascending k, so a pair's result does not depend on what else is in the batch or
@@ -38,32 +38,58 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
-// h: [n_tokens, width] activation type; router: [experts, width] float32; one warp per token.
+__device__ __forceinline__ void ld4_f32(const float* p, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+__device__ __forceinline__ void ld4_f32(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 x = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&x.x), b = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+
+constexpr int kMoeRouteWarps = 8;
+
+// h: [n_tokens, width] activation type; router: [experts, width] float32; one block per token.  Every warp
+// forms the logits of its share of the experts (a lane sums its elements in ascending order, the lanes are
+// added up by a butterfly: the same sum whatever else the step holds); the first warp makes the choice.
 template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router,
-                                 const float* __restrict__ correction, int* __restrict__ chosen,
-                                 float* __restrict__ weights, int n_tokens, int width, int experts, int n_groups,
-                                 int keep, int top) {
+__global__ void __launch_bounds__(kMoeRouteWarps * 32)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router,
+                 const float* __restrict__ correction, int* __restrict__ chosen,
+                 float* __restrict__ weights, int n_tokens, int width, int experts, int n_groups,
+                 int keep, int top) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= n_tokens) return;
-  float* s = smem + (size_t)warp * (2 * experts + n_groups);
+  const int t = blockIdx.x;
+  float* s = smem;
   float* c = s + experts;
   float* gs = c + experts;
   const T* x = h + (size_t)t * width;
-  for (int e = 0; e < experts; ++e) {
+  const bool vec = (width & 3) == 0 && (reinterpret_cast<uintptr_t>(h) & (4 * sizeof(T) - 1)) == 0 &&
+                   (reinterpret_cast<uintptr_t>(router) & 15) == 0;
+  for (int e = warp; e < experts; e += kMoeRouteWarps) {
     const float* w = router + (size_t)e * width;
     float acc = 0.0f;
-    for (int i = lane; i < width; i += 32) acc += to_f32<T>(x[i]) * w[i];
+    if (vec) {
+      for (int i = lane * 4; i < width; i += 128) {
+        float xv[4], wv[4];
+        ld4_f32(x + i, xv); ld4_f32(w + i, wv);
+        acc += xv[0] * wv[0]; acc += xv[1] * wv[1]; acc += xv[2] * wv[2]; acc += xv[3] * wv[3];
+      }
+    } else {
+      for (int i = lane; i < width; i += 32) acc += to_f32<T>(x[i]) * w[i];
+    }
     acc = warp_sum(acc);
     if (lane == 0) {
       s[e] = 1.0f / (1.0f + expf(-acc));
       c[e] = s[e] + (correction != nullptr ? correction[e] : 0.0f);
     }
   }
+  __syncthreads();
+  if (warp != 0) return;
   __syncwarp();
   const int size = experts / n_groups;
   if (keep < n_groups) {
@@ -292,11 +318,10 @@ TK_API int tk_moe_route(const void* h, const float* router, const float* correct
       top < 1 || top > keep * (experts / n_groups)) {
     return (int)cudaErrorInvalidValue;
   }
-  const int warps = 4;
-  const size_t smem = (size_t)warps * (2 * experts + n_groups) * sizeof(float);
+  const size_t smem = (size_t)(2 * experts + n_groups) * sizeof(float);
   cudaError_t e = cudaSuccess;
-  TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::moe_route_kernel<T>, dim3((unsigned)((n_tokens + warps - 1) / warps)),
-                                             dim3(warps * 32), smem, stream, (const T*)h, router, correction, chosen,
+  TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::moe_route_kernel<T>, dim3((unsigned)n_tokens),
+                                             dim3(tk::kMoeRouteWarps * 32), smem, stream, (const T*)h, router, correction, chosen,
                                              weights, n_tokens, width, experts, n_groups, keep, top));
   if (e != cudaSuccess) return (int)e;
   e = tk::launch(tk::moe_sort_kernel, dim3(1), dim3(1024), 0, stream, (const int*)chosen, order, tiles, n_tiles,

@@ -985,10 +985,12 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                      req_slot: torch.Tensor, block_table: torch.Tensor, err: torch.Tensor, *,
                      scale: float, window: int | None, n_splits: int,
                      scratch: torch.Tensor | None = None, softcap: float | None = None,
-                     sinks: torch.Tensor | None = None) -> None:
+                     sinks: torch.Tensor | None = None, chunk: int | None = None,
+                     slopes: torch.Tensor | None = None) -> None:
     """Split-K paged attention for the single next tokens listed in ``items`` (bfloat16 only).
-    ``softcap`` and ``sinks`` as in :func:`attention_plain`."""
+    ``softcap``, ``sinks``, ``chunk`` and ``slopes`` as in :func:`attention_plain`."""
     _want_sinks(sinks, q.shape[1])
+    _want_sinks(slopes, q.shape[1])
     _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")
     _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
     _want(items, torch.int32, "items")
@@ -1013,7 +1015,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                                          block_table.data_ptr(), err.data_ptr(), n_items,
                                          req_slot.numel(), hq, hkv, d, page_size, block_table.shape[1],
                                          num_pages, int(window or 0), n_splits, float(scale),
-                                         float(softcap or 0.0), _ptr(sinks), _stream()),
+                                         float(softcap or 0.0), _ptr(sinks), int(chunk or 0), _ptr(slopes),
+                                         _stream()),
            "attention_decode")
 
 
@@ -1063,11 +1066,13 @@ def attention_decode_balanced(q: torch.Tensor, out: torch.Tensor, k_cache: torch
                               items: torch.Tensor, positions: torch.Tensor, tok_req: torch.Tensor,
                               req_slot: torch.Tensor, block_table: torch.Tensor, err: torch.Tensor, *,
                               scale: float, window: int | None, blocks: int, softcap: float | None = None,
-                              sinks: torch.Tensor | None = None) -> None:
+                              sinks: torch.Tensor | None = None, chunk: int | None = None,
+                              slopes: torch.Tensor | None = None) -> None:
     """Paged attention for the single next tokens listed in ``items`` (bfloat16 only), the key tiles of
-    all (token, kv head) pairs dealt out evenly over ``blocks`` blocks.  ``softcap`` and ``sinks`` as in
-    :func:`attention_plain`."""
+    all (token, kv head) pairs dealt out evenly over ``blocks`` blocks.  ``softcap``, ``sinks``, ``chunk``
+    and ``slopes`` as in :func:`attention_plain`."""
     _want_sinks(sinks, q.shape[1])
+    _want_sinks(slopes, q.shape[1])
     _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")
     _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
     _want(items, torch.int32, "items")
@@ -1092,7 +1097,7 @@ def attention_decode_balanced(q: torch.Tensor, out: torch.Tensor, k_cache: torch
                                             block_table.data_ptr(), err.data_ptr(), n_items, req_slot.numel(),
                                             hq, hkv, d, page_size, block_table.shape[1], num_pages,
                                             int(window or 0), blocks, float(scale), float(softcap or 0.0),
-                                            _ptr(sinks), _stream()),
+                                            _ptr(sinks), int(chunk or 0), _ptr(slopes), _stream()),
            "attention_decode_balanced")
 
 
@@ -1215,7 +1220,8 @@ def _prefill_tc_workspace(device: torch.device, part_slots: int, counters: int, 
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                          items: PrefillItems, block_table: torch.Tensor, err: torch.Tensor, *,
                          scale: float, window: int | None, softcap: float | None = None,
-                         sinks: torch.Tensor | None = None) -> None:
+                         sinks: torch.Tensor | None = None, chunk: int | None = None,
+                         slopes: torch.Tensor | None = None) -> None:
     """Paged flash attention on tcgen05 for the work list ``items`` (see :func:`prefill_tc_records`),
     a persistent kernel that deals the items out to one block per SM.  Loads whole pages: the cache
     must have been written by :func:`rope_kv` with ``req_q_len`` and ``req_kv_len`` given.  One call
@@ -1238,7 +1244,8 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tens
                                           ws["sched"].data_ptr(), part_o, part_ml, ws["count"].data_ptr(),
                                           n, items.records.shape[0], hq, hkv, d, page_size,
                                           block_table.shape[1], num_pages, int(window or 0),
-                                          float(scale), float(softcap or 0.0), _ptr(sinks), _stream()),
+                                          float(scale), float(softcap or 0.0), _ptr(sinks), int(chunk or 0),
+                                          _ptr(slopes), _stream()),
            "attention_prefill_tc")
 
 

@@ -75,8 +75,14 @@ __global__ void hgrn2_prepare_kernel(StackedInput in, int q_off, int f_off, int 
   prep_qka(l, h, t, e, zq * sigmoidf_(zq), 1.0f - f, f);
 }
 
-// One thread per (request, head) walks the request's tokens: gates[t, h] = (alpha, exp(i - m_t), exp(-m_t)),
-// and the running maximum in the slot's record moves on.
+// One warp per (request, head) walks the request's tokens, 32 * kMlstmPerLane at a time:
+// gates[t, h] = (alpha, exp(i - m_t), exp(-m_t)), and the running maximum in the slot's record moves on.
+// A token is the map m -> max(a + m, b) with a = f, b = i; maps compose to maps of the same form,
+// (a2, b2) after (a1, b1) = (a1 + a2, max(a2 + b1, b2)), so the maxima of a stretch come from a scan: every lane
+// composes its own consecutive tokens, the lanes' maps are scanned with shuffles, and each lane then walks
+// its tokens again from the maximum that precedes them.
+constexpr int kMlstmPerLane = 4;
+
 template <typename T>
 __global__ void mlstm_gates_kernel(StackedInput in, int i_off, int f_off, const float* __restrict__ i_bias,
                                    const float* __restrict__ f_bias, float cap, float* __restrict__ m_state,
@@ -85,25 +91,55 @@ __global__ void mlstm_gates_kernel(StackedInput in, int i_off, int f_off, const 
                                    int n_tokens, int n_reqs, int n_slots, int heads) {
   pdl_trigger();
   pdl_wait();
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (idx >= n_reqs * heads) return;
   const int r = idx / heads, h = idx - r * heads;
   const int slot = req_slot[r], q0 = req_q_start[r], n = req_q_len[r];
-  if (slot < 0 || slot >= n_slots || q0 < 0 || n < 0 || q0 + n > n_tokens) { set_error(err, kErrRequest, r, slot, q0); return; }
-  float m = m_state[(size_t)slot * heads + h];
-  const float inv_cap = 1.0f / cap, bi = i_bias[h], bf = f_bias[h];
-  for (int t = q0; t < q0 + n; ++t) {
-    const size_t row = (size_t)t * in.row_stride;
-    const float gi = cap * tanhf((stacked_ld<T>(in, row + i_off + h) + bi) * inv_cap);
-    const float gf = log_sigmoidf_(cap * tanhf((stacked_ld<T>(in, row + f_off + h) + bf) * inv_cap));
-    const float m_new = fmaxf(gf + m, gi);
-    float* g = gates + ((size_t)t * heads + h) * 3;
-    g[0] = expf(gf + m - m_new);
-    g[1] = expf(gi - m_new);
-    g[2] = expf(-m_new);
-    m = m_new;
+  if (slot < 0 || slot >= n_slots || q0 < 0 || n < 0 || q0 + n > n_tokens) {
+    if (lane == 0) set_error(err, kErrRequest, r, slot, q0);
+    return;
   }
-  m_state[(size_t)slot * heads + h] = m;
+  float m = m_state[(size_t)slot * heads + h];          // the maximum before the stretch, the same in every lane
+  const float inv_cap = 1.0f / cap, bi = i_bias[h], bf = f_bias[h];
+  for (int base = 0; base < n; base += 32 * kMlstmPerLane) {
+    const int t0 = q0 + base + lane * kMlstmPerLane;
+    float gi[kMlstmPerLane], gf[kMlstmPerLane];
+    float a = 0.0f, b = -INFINITY;                      // the lane's tokens as one map; (0, -inf) changes nothing
+#pragma unroll
+    for (int j = 0; j < kMlstmPerLane; ++j) {
+      if (t0 + j < q0 + n) {
+        const size_t row = (size_t)(t0 + j) * in.row_stride;
+        gi[j] = cap * tanhf((stacked_ld<T>(in, row + i_off + h) + bi) * inv_cap);
+        gf[j] = log_sigmoidf_(cap * tanhf((stacked_ld<T>(in, row + f_off + h) + bf) * inv_cap));
+        b = fmaxf(gf[j] + b, gi[j]);
+        a += gf[j];
+      }
+    }
+    // inclusive scan of the lanes' maps
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float pa = __shfl_up_sync(0xffffffffu, a, o);
+      const float pb = __shfl_up_sync(0xffffffffu, b, o);
+      if (lane >= o) { b = fmaxf(a + pb, b); a += pa; }
+    }
+    // the maximum in front of this lane's tokens: the lanes before it applied to m
+    float ea = __shfl_up_sync(0xffffffffu, a, 1), eb = __shfl_up_sync(0xffffffffu, b, 1);
+    float mj = lane == 0 ? m : fmaxf(ea + m, eb);
+#pragma unroll
+    for (int j = 0; j < kMlstmPerLane; ++j) {
+      if (t0 + j < q0 + n) {
+        const float m_new = fmaxf(gf[j] + mj, gi[j]);
+        float* g = gates + ((size_t)(t0 + j) * heads + h) * 3;
+        g[0] = expf(gf[j] + mj - m_new);
+        g[1] = expf(gi[j] - m_new);
+        g[2] = expf(-m_new);
+        mj = m_new;
+      }
+    }
+    m = __shfl_sync(0xffffffffu, fmaxf(a + m, b), 31);
+  }
+  if (lane == 0) m_state[(size_t)slot * heads + h] = m;
 }
 
 // l.dv counts the column of ones: the values proper are l.dv - 1 wide.
@@ -252,7 +288,7 @@ TK_API int tk_mlstm_prepare(const void* x, const float* parts, int n_parts, long
   const tk::StackedInput in = stacked(x, parts, n_parts, part_stride, row_stride);
   const tk::PrepLayout l = layout(prep, n_tokens, heads, dk, dv + 1);
   cudaError_t e = cudaSuccess;
-  TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::mlstm_gates_kernel<T>, dim3((unsigned)((n_reqs * heads + 63) / 64)),
+  TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::mlstm_gates_kernel<T>, dim3((unsigned)((n_reqs * heads + 1) / 2)),
                                              dim3(64), 0, stream, in, i_off, f_off, i_bias, f_bias, cap, m_state, gates,
                                              req_q_start, req_q_len, req_slot, err, n_tokens, n_reqs, n_slots, heads));
   if (e != cudaSuccess) return (int)e;

@@ -413,8 +413,8 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     ``softcap`` bounds the scaled scores by ``cap * tanh(score / cap)``; ``sinks`` (float32, one per
     query head) adds ``exp(sink)`` to every softmax denominator.  ``out`` is ``[N, Hq, dv]`` where
     the value heads have a size of their own.  ``chunk`` (a query sees only its own block of that many
-    positions) and ``slopes`` (a distance bias per query head) are known to the general kernel, which
-    then runs every token of the step.
+    positions) and ``slopes`` (a distance bias per query head) are known to the general kernel, the decode
+    kernels and the tcgen05 prefill kernel.
 
     Chooses the kernels.  A latent cache in bfloat16 goes to the tensor-core kernel that stacks the heads
     of a token (``csrc/attention_latent.cu``).  bfloat16 with a head_dim the tiled kernels take: single next
@@ -423,11 +423,6 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     and every other shape, runs on the general kernel.
     """
     ops.flush_chains()     # q and the pages may come from a product that is still queued: launch it on this stream
-    if chunk is not None or slopes is not None:
-        ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req, step.req_slot,
-                            cache_view.table, step.err, scale=scale, window=window, softcap=softcap, sinks=sinks,
-                            chunk=chunk, slopes=slopes)
-        return
     n, hq, d = q.shape
     hkv, page = cache_view.k.shape[1], cache_view.k.shape[2]
     bf16 = q.dtype == torch.bfloat16
@@ -449,7 +444,9 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     # the tiled kernels take heads of one size for keys and values; of the two prefill kernels the
     # tcgen05 one knows caps and sinks
     same_size = cache_view.v.shape[3] == d
-    extras = softcap is not None or sinks is not None
+    extras = softcap is not None or sinks is not None or chunk is not None or slopes is not None
+    # a single token sees no more keys than its chunk holds: the kernels' work is planned for that many
+    dec_span = step.max_kv_len if chunk is None else min(step.max_kv_len, chunk)
     dec_tiled = bf16 and n_dec > 0 and same_size and ops.decode_kernel_takes(hq, hkv, d, page)
     pf_tiled = (bf16 and n_pf > 0 and same_size and ops.prefill_kernel_takes(hq, hkv, d, page)
                 and (not extras or ops.prefill_tc_kernel_takes(hq, hkv, d, page)))
@@ -463,22 +460,22 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
         side.wait_event(fork)
     if dec_tiled:
         with torch.cuda.stream(side) if beside else contextlib.nullcontext():
-            if ops.decode_uses_balanced(q.device, n_dec, hkv, step.max_kv_len):
+            if ops.decode_uses_balanced(q.device, n_dec, hkv, dec_span):
                 ops.attention_decode_balanced(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
                                               step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
-                                              window=window, softcap=softcap, sinks=sinks,
-                                              blocks=ops.decode_balanced_blocks(q.device, n_dec, hkv, step.max_kv_len))
+                                              window=window, softcap=softcap, sinks=sinks, chunk=chunk, slopes=slopes,
+                                              blocks=ops.decode_balanced_blocks(q.device, n_dec, hkv, dec_span))
             else:
                 ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
                                      step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
-                                     window=window, softcap=softcap, sinks=sinks,
-                                     n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
+                                     window=window, softcap=softcap, sinks=sinks, chunk=chunk, slopes=slopes,
+                                     n_splits=ops.decode_splits(n_dec, hkv, dec_span))
             if beside:
                 join.record()
     if pf_tiled and ops.prefill_tc_kernel_takes(hq, hkv, d, page):
         ops.attention_prefill_tc(q, out, cache_view.k, cache_view.v, step.prefill_tc,
                                  cache_view.table, step.err, scale=scale, window=window, softcap=softcap,
-                                 sinks=sinks)
+                                 sinks=sinks, chunk=chunk, slopes=slopes)
     elif pf_tiled:
         ops.attention_prefill(q, out, cache_view.k, cache_view.v, step.prefill_tiles,
                               step.req_q_start, step.req_q_len, step.req_kv_len, step.req_slot,
@@ -491,4 +488,4 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
         items = None if (dec_rest and pf_rest) else (step.decode_items if dec_rest else step.prefill_items)
         ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req,
                             step.req_slot, cache_view.table, step.err, scale=scale, window=window,
-                            items=items, softcap=softcap, sinks=sinks)
+                            items=items, softcap=softcap, sinks=sinks, chunk=chunk, slopes=slopes)
