@@ -542,8 +542,17 @@ def test_mlstm_running_maximum_over_long_portions(dtype):
     got = run_in_steps(seqs, [3, 0], cuts, lambda rows, step: torch.as_tensor(
         part.forward(dev(rows), step, view)).float().reshape(-1, rows.shape[0], width).sum(0))
     m = {"heads": heads, "dim": dk, "vdim": dv, "gate_cap": cap}
-    for g, x in zip(got, seqs):
-        close(g, plain.mlstm_mixer(x.double(), {k: v.double() for k, v in w.items()}, m, 1e-6), dtype, scale=3.0)
+    # Hundreds of tokens with a head whose memory stays tiny: the unit norm magnifies what 16-bit products cost,
+    # so bfloat16 is judged against the plain implementation rounding where an engine of 16 bits rounds.
+    keep = plain.ROUND
+    try:
+        if dtype == "bfloat16":
+            plain.ROUND = lambda t: t.to(torch.bfloat16).double()
+        want = [plain.mlstm_mixer(x.double(), {k: v.double() for k, v in w.items()}, m, 1e-6) for x in seqs]
+    finally:
+        plain.ROUND = keep
+    for g, x in zip(got, want):
+        close(g, x, dtype, scale=3.0)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
