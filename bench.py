@@ -1158,15 +1158,15 @@ def tarivik_config(s: dict) -> dict:
     w, d = s["width"], s["dim"]
     left = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5,
             "mask": {"size": s["window"]}}
-    right = {"heads": w // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 2}
-    par = {"left": left, "right": right, "left_scale": 0.8, "right_scale": 0.5}
+    right = {"heads": w // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 4}
+    par = {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.6}
     rec = {"heads": w // 256, "dim": 128, "vdim": 256}
     mlp = {"kind": "moe", "expert": {"ff": s["ff"] // 2},
            "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}
     order = [("parallel", par), ("hgrn2", rec), ("parallel", par), ("mlstm", dict(rec, gate_cap=15.0))]
     layers = [{"type": order[i % 4][0], "mixer": order[i % 4][1], "mlp": mlp} for i in range(s["layers"])]
     return {"architecture": "Tarivik", "vocab": s["vocab"], "width": w, "max_positions": 32768,
-            "norm": {"eps": 1e-6, "groups": 4}, "canon": {"taps": 4}, "layers": layers}
+            "norm": {"eps": 1e-5, "groups": 8}, "canon": {"taps": 4}, "layers": layers}
 
 
 def tarivik_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> list[dict]:
@@ -1294,7 +1294,7 @@ def tarivik_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
         wd = bf(experts, width, ffe) * ffe ** -0.5
         route = lambda: ops.moe_route(h, router, corr, top=top, n_groups=4, keep=2, padded=True)
         routing = route()
-        row(f"router (scores, groups, choice, tiles), {name}", None, _time_us(route, graph=False), 0.0,
+        row(f"router (scores, groups, choice, tiles), {name}", None, _time_us(route, graph=True), 0.0,
             nbytes=n * width * 2 + experts * width * 4)
         wgu_dense = bf(2 * top * ffe, width) * width ** -0.5
         wd_dense = bf(width, top * ffe) * (top * ffe) ** -0.5
@@ -1312,7 +1312,10 @@ def tarivik_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
             return y
         used = len(set(routing.chosen.flatten().tolist()))
         wgu = ops.moe_stack_gate_up(wg, wu)
-        moe = lambda: ops.moe_experts_tc(h, routing, wgu, wd, err)
+        if ops.moe_small_takes(n, top, width, ffe):       # as the part chooses
+            moe = lambda: ops.moe_experts_small(h, routing, wgu, wd)
+        else:
+            moe = lambda: ops.moe_experts_tc(h, routing, wgu, wd, err)
         flops = 2.0 * n * top * 3 * ffe * width
         if single:
             row(f"experts (gate, up, down, weighted sum), {name}", "dense gated unit of the same active width",

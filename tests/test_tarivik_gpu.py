@@ -209,6 +209,36 @@ def test_input_convolution_across_steps_slots_and_single_tokens(dtype, taps):
         assert torch.isnan(tail[1]).all()                       # nobody's slot is nobody's business
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("taps,width", [(2, 64), (4, 520), (7, 36)])
+def test_input_convolution_in_steps_of_many_tokens(dtype, taps, width):
+    """Steps of 64 tokens and more, where a thread forms several tokens of four channels: requests that begin
+    and end anywhere inside such a group of tokens, single tokens among long portions, a request whose window
+    reaches back into the tail for its first tokens; bit for bit the results of the steps of few tokens."""
+    from tokamak_b200.csrc import ops
+    gen = torch.Generator().manual_seed(taps * width)
+    w = torch.randn(width, taps, generator=gen) * 0.5
+    cuts = [[70, 1, 3, 129, 2], [3, 66, 1, 1, 70], [1, 0, 61, 5, 9]]
+    slots = [2, 0, 3]
+    seqs = [torch.randn(sum(c), width, generator=gen).to(TORCH[dtype]).float() for c in cuts]
+
+    def run(cuts_of):
+        tail = torch.full((4, taps - 1, width), float("nan"), device="cuda")
+        tail[slots] = 0.0
+        got = run_in_steps(seqs, slots, cuts_of, lambda rows, step: ops.short_conv(
+            dev(rows), dev(w), tail, step, dtype=TORCH[dtype], add_input=True))
+        return got, tail
+    got, tail = run(cuts)
+    for g, x in zip(got, seqs):
+        close(g, plain.input_conv(x.double(), w.double()), dtype)
+    for r, slot in enumerate(slots):
+        assert torch.equal(tail[slot].cpu(), seqs[r][-(taps - 1):])
+    assert torch.isnan(tail[1]).all()
+    small, _ = run([[7] * (len(x) // 7) + [len(x) % 7] for x in seqs])      # every step below 64 tokens
+    for a, b in zip(got, small):
+        assert torch.equal(a, b)
+
+
 def _ref_moe(h, w, m):
     return plain.moe(h.double(), {k: v.double() for k, v in w.items()}, m)
 
@@ -296,6 +326,39 @@ def test_mixture_of_experts_on_the_tensor_cores(n, width, ff, experts, count, ke
     pick = torch.randperm(n, generator=gen)[:max(1, n // 3)]
     again = ops.moe_experts_tc(dev(h[pick]), route(h[pick]), gate_up, down, err)
     assert torch.equal(again.cpu(), got.cpu()[pick])
+    assert err.tolist()[0] == 0
+
+
+@pytest.mark.parametrize("n,width,ff,experts,count,keep,top", [(1, 72, 64, 4, 1, 1, 2), (8, 256, 320, 16, 4, 2, 2),
+                                                                (16, 64, 128, 2, 1, 1, 2), (5, 136, 192, 9, 3, 3, 4),
+                                                                (10, 64, 64, 3, 1, 1, 3), (3, 520, 1088, 8, 4, 2, 2)])
+def test_mixture_of_experts_in_steps_of_few_tokens(monkeypatch, n, width, ff, experts, count, keep, top):
+    """bfloat16 steps of few tokens, where the chosen experts' weights are streamed once: experts nobody
+    chose, experts chosen by more tokens than are worked on at a time (every token takes every expert), rows
+    longer than one sweep of a warp; a token's result is the same bit for bit whatever else is in the step.
+    The kernel is tried beyond the number of pairs up to which the engine prefers it."""
+    from tokamak_b200.csrc import ops
+    monkeypatch.setattr(ops, "MOE_SMALL_PAIRS", 64)
+    gen = torch.Generator().manual_seed(n * 7 + width)
+    rnd = lambda *s, std=1.0: (torch.randn(*s, generator=gen) * std).to(torch.bfloat16)
+    h = rnd(n, width)
+    w = {"router": rnd(experts, width, std=0.3).float(), "correction": torch.randn(experts, generator=gen) * 0.1}
+    for e in range(experts):
+        w[f"e{e}.gate"], w[f"e{e}.up"], w[f"e{e}.down"] = rnd(ff, width, std=0.2), rnd(ff, width, std=0.2), rnd(width, ff, std=0.2)
+    m = {"router": {"experts": experts, "top": top, "groups": {"count": count, "keep": keep}}}
+    stack = lambda name: dev(torch.stack([w[f"e{e}.{name}"] for e in range(experts)]))
+    assert ops.moe_small_takes(n, top, width, ff)
+    gate_up, down = ops.moe_stack_gate_up(stack("gate"), stack("up")), stack("down")
+    route = lambda x: ops.moe_route(dev(x), dev(w["router"]), dev(w["correction"]), top=top, n_groups=count, keep=keep,
+                                    padded=True)
+    got = ops.moe_experts_small(dev(h), route(h), gate_up, down)
+    close(got, _ref_moe(h, w, m), "bfloat16", scale=2.0)
+    for keep_rows in (slice(0, 1), slice(n // 2, n), torch.randperm(n, generator=gen)):
+        again = ops.moe_experts_small(dev(h[keep_rows]), route(h[keep_rows]), gate_up, down)
+        assert torch.equal(again.cpu(), got.cpu()[keep_rows])
+    # and beside the tensor-core path over the same weights, which rounds elsewhere
+    err = torch.zeros(4, dtype=torch.int32, device="cuda")
+    close(ops.moe_experts_tc(dev(h), route(h), gate_up, down, err), got.cpu().double(), "bfloat16", scale=2.0)
     assert err.tolist()[0] == 0
 
 
@@ -537,7 +600,7 @@ def test_mlstm_running_maximum_over_long_portions(dtype):
     w["i.b"] = torch.tensor([3.0, -9.0])
     part = _mixer_part("mlstm", MlstmSpec(width, heads, dk, dv, cap, 1e-6), w, dtype)
     view = _state_views(part)
-    cuts = [[150, 1, 137, 1, 2], [1, 301, 0, 130, 1]]
+    cuts = [[150, 1, 137, 1, 2], [1, 1101, 0, 530, 1]]
     seqs = [torch.randn(sum(c), width, generator=gen).to(TORCH[dtype]) for c in cuts]
     got = run_in_steps(seqs, [3, 0], cuts, lambda rows, step: torch.as_tensor(
         part.forward(dev(rows), step, view)).float().reshape(-1, rows.shape[0], width).sum(0))

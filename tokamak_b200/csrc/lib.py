@@ -77,6 +77,8 @@ _SIGNATURES: dict[str, list] = {
     "tk_moe_combine_rows": [_P, _P, _P, _P, c_int, c_int, c_int, _P],
     "tk_moe_ffn": [_P, c_longlong, c_int, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_moe_combine": [_P, _P, _P, c_int, c_int, c_int, _P],
+    "tk_moe_small_max_pairs": [],
+    "tk_moe_small": [_P, c_longlong, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_qkv_pairs": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                      c_float, c_int, _P],

@@ -303,6 +303,210 @@ __global__ void moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ y, con
   reinterpret_cast<float2*>(out + (size_t)t * width)[c] = make_float2(a0, a1);
 }
 
+// ---- steps of few tokens: the chosen experts' weights are streamed once by the CUDA cores
+//
+// The output rows of the experts that some pair chose, one expert after the other, are dealt out evenly to
+// a grid that fills the GPU once, so the load is even whatever the number of chosen experts, and an expert
+// that nobody chose is not read.  For a stretch of an expert's rows a block lists the pairs that chose the
+// expert, stages their input rows in shared memory (kMoeSmallRows at a time), and every warp forms whole
+// output rows: a lane brings 16-byte pieces of the weight row into a ring of its own in shared memory by
+// asynchronous copies, kMoeSmallStages - 1 stages of kMoeSmallPieces pieces ahead (what is under way is
+// bounded by shared memory, not by registers), adds its products to four running sums in a fixed order, and the lanes are
+// added up by a butterfly: a pair's result does not depend on what else is in the step.  Gated: the gate
+// and up rows of output n lie in a stacked matrix [experts, 2 n_out, k] in alternating blocks of `block` rows.
+constexpr int kMoeSmallRows = 4;
+constexpr int kMoeSmallWarps = 8;
+constexpr int kMoeSmallStages = 4;
+constexpr int kMoeSmallPieces = 4;            // 16-byte pieces of a lane and stage
+constexpr int kMoeSmallMaxPairs = 64;
+constexpr int kMoeSmallRing = kMoeSmallWarps * kMoeSmallStages * kMoeSmallPieces * 32 * 16;      // bytes
+
+struct MoeSmallParams {
+  const __nv_bfloat16* a;       // input rows; pair i reads row i / a_div
+  long long a_stride;
+  int a_div;
+  const __nv_bfloat16* b;       // [experts, n_out, k], or the stacked gate/up matrix
+  void* out;                    // gated: bfloat16 [pairs, n_out]; else float32 [pairs, n_out]
+  const int* chosen;            // [pairs]
+  int pairs, experts, n_out, k, act, block;
+};
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 x = __bfloat1622float2(h[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+}
+__device__ __forceinline__ void small_cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void small_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void small_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(kMoeSmallStages - 1) : "memory");
+}
+
+// Rows n_begin + warp, + kMoeSmallWarps, ... < n_end of expert e for `count` <= R staged input rows.
+// A warp's work is the sequence of (row, stage) items; item i + kMoeSmallStages - 1 is asked for before
+// item i is worked through.  ring: this lane's first piece; pieces of a stage are 512 bytes apart.
+template <int R, bool kGated>
+__device__ __forceinline__ void moe_small_rows(const MoeSmallParams& p, const __nv_bfloat16* xs, uint4* ring,
+                                               const int* mine, int count, int e, int n_begin, int n_end) {
+  constexpr int kSweeps = kGated ? kMoeSmallPieces / 2 : kMoeSmallPieces;     // sweeps of the warp over k in a stage
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int per_row = (p.k + kSweeps * 256 - 1) / (kSweeps * 256);
+  const int n_rows = n_end > n_begin + warp ? (n_end - n_begin - warp + kMoeSmallWarps - 1) / kMoeSmallWarps : 0;
+  const int items = n_rows * per_row;
+  const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring);
+  auto ask = [&](int item) {
+    if (item < items) {
+      const int row = item / per_row, k0 = (item - row * per_row) * kSweeps * 256 + lane * 8;
+      const int n = n_begin + warp + row * kMoeSmallWarps;
+      const __nv_bfloat16* w0;
+      if (kGated) {
+        const int j = n / p.block, i = n - j * p.block;
+        w0 = p.b + ((size_t)e * 2 * p.n_out + (size_t)(2 * j) * p.block + i) * p.k;
+      } else {
+        w0 = p.b + ((size_t)e * p.n_out + n) * p.k;
+      }
+      const uint32_t dst = ring_u32 + (uint32_t)(item % kMoeSmallStages) * (kMoeSmallPieces * 512);
+#pragma unroll
+      for (int u = 0; u < kSweeps; ++u) {
+        const int kk = k0 + u * 256;
+        if (kk < p.k) {
+          small_cp16(dst + u * 512, w0 + kk);
+          if (kGated) small_cp16(dst + (kSweeps + u) * 512, w0 + (size_t)p.block * p.k + kk);
+        }
+      }
+    }
+    small_commit();
+  };
+  for (int i = 0; i < kMoeSmallStages - 1; ++i) ask(i);
+  float acc0[R][4], acc1[R][4];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { acc0[r][i] = 0.0f; acc1[r][i] = 0.0f; }
+  }
+  for (int item = 0; item < items; ++item) {
+    ask(item + kMoeSmallStages - 1);
+    small_wait();
+    const int row = item / per_row, part = item - row * per_row;
+    const int k0 = part * kSweeps * 256 + lane * 8;
+    const uint4* src = ring + (size_t)(item % kMoeSmallStages) * (kMoeSmallPieces * 32);
+#pragma unroll
+    for (int u = 0; u < kSweeps; ++u) {
+      const int kk = k0 + u * 256;
+      if (kk < p.k) {
+        float wa[8], wb[8];
+        unpack8(src[u * 32], wa);
+        if (kGated) unpack8(src[(kSweeps + u) * 32], wb);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          if (r < count) {
+            float xv[8];
+            unpack8(*reinterpret_cast<const uint4*>(xs + (size_t)r * p.k + kk), xv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {       // four running sums a row, so that no product waits for the one before
+              acc0[r][i & 3] += xv[i] * wa[i];
+              if (kGated) acc1[r][i & 3] += xv[i] * wb[i];
+            }
+          }
+        }
+      }
+    }
+    if (part + 1 < per_row) continue;
+    const int n = n_begin + warp + row * kMoeSmallWarps;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (r < count) {              // (the same for every lane)
+        const float s0 = warp_sum((acc0[r][0] + acc0[r][1]) + (acc0[r][2] + acc0[r][3]));
+        const float s1 = kGated ? warp_sum((acc1[r][0] + acc1[r][1]) + (acc1[r][2] + acc1[r][3])) : 0.0f;
+        if (lane == 0) {
+          const size_t at = (size_t)mine[r] * p.n_out + n;
+          if (kGated) ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(glu_act(s0, p.act) * s1);
+          else ((float*)p.out)[at] = s0;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { acc0[r][i] = 0.0f; acc1[r][i] = 0.0f; }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
+template <bool kGated>
+__global__ void __launch_bounds__(kMoeSmallWarps * 32) moe_small_kernel(MoeSmallParams p) {
+  extern __shared__ __align__(16) unsigned char small_smem[];      // the warps' rings, then the staged input rows
+  __shared__ unsigned live_bits[kMoeMaxExperts / 32];
+  __shared__ int live_ids[kMoeSmallMaxPairs], mine[kMoeSmallMaxPairs], chosen_s[kMoeSmallMaxPairs];
+  __shared__ int n_live_s, total_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint4* ring = reinterpret_cast<uint4*>(small_smem) + (size_t)warp * kMoeSmallStages * kMoeSmallPieces * 32 + lane;
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(small_smem + kMoeSmallRing);
+  pdl_trigger();
+  if (threadIdx.x < kMoeMaxExperts / 32) live_bits[threadIdx.x] = 0u;
+  __syncthreads();
+  pdl_wait();
+  // the experts that were chosen, in ascending order
+  if (threadIdx.x < p.pairs) {
+    const int e = p.chosen[threadIdx.x];
+    chosen_s[threadIdx.x] = e;
+    if (e >= 0 && e < p.experts) atomicOr(&live_bits[e >> 5], 1u << (e & 31));
+  }
+  __syncthreads();
+  if (warp == 0) {
+    unsigned word = live_bits[lane];
+    const int c = __popc(word);
+    int before = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, before, o);
+      if (lane >= o) before += up;
+    }
+    if (lane == 31) n_live_s = before;
+    before -= c;
+    while (word != 0u) {
+      const int bit = __ffs(word) - 1;
+      live_ids[before++] = lane * 32 + bit;
+      word &= word - 1u;
+    }
+  }
+  __syncthreads();
+  const long long all_rows = (long long)n_live_s * p.n_out;
+  long long g = all_rows * blockIdx.x / gridDim.x;
+  const long long g_end = all_rows * (blockIdx.x + 1) / gridDim.x;
+  const int k16 = p.k / 8;
+  while (g < g_end) {
+    const int rank = (int)(g / p.n_out), n_begin = (int)(g - (long long)rank * p.n_out);
+    const int n_end = (int)min((long long)p.n_out, n_begin + (g_end - g));
+    const int e = live_ids[rank];
+    if (warp == 0) {
+      int total = 0;
+      for (int base = 0; base < p.pairs; base += 32) {
+        const bool m = base + lane < p.pairs && chosen_s[base + lane] == e;
+        const unsigned votes = __ballot_sync(0xffffffffu, m);
+        if (m) mine[total + __popc(votes & ((1u << lane) - 1u))] = base + lane;
+        total += __popc(votes);
+      }
+      if (lane == 0) total_s = total;
+    }
+    __syncthreads();
+    const int total = total_s;
+    for (int first = 0; first < total; first += kMoeSmallRows) {
+      const int count = min(kMoeSmallRows, total - first);
+      for (int i = threadIdx.x; i < count * k16; i += blockDim.x) {
+        const int r = i / k16, c = i - r * k16;
+        reinterpret_cast<uint4*>(xs)[(size_t)r * k16 + c] =
+            reinterpret_cast<const uint4*>(p.a + (size_t)(mine[first + r] / p.a_div) * p.a_stride)[c];
+      }
+      __syncthreads();
+      if (count <= 2) moe_small_rows<2, kGated>(p, xs, ring, mine + first, count, e, n_begin, n_end);
+      else moe_small_rows<4, kGated>(p, xs, ring, mine + first, count, e, n_begin, n_end);
+      __syncthreads();
+    }
+    g += n_end - n_begin;
+  }
+}
+
 }  // namespace tk
 
 TK_API int tk_moe_tile_rows() { return tk::kMoeTileRows; }
@@ -375,4 +579,44 @@ TK_API int tk_moe_combine(const float* y, const float* weights, float* out, int 
   const long long total = (long long)n_tokens * width;
   return (int)tk::launch(tk::moe_combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, y, weights,
                          out, n_tokens, width, top);
+}
+
+TK_API int tk_moe_small_max_pairs() { return tk::kMoeSmallMaxPairs; }
+
+// bfloat16.  block > 0: b is the stacked gate/up matrix [experts, 2 n_out, k] (alternating blocks of `block`
+// rows), out[pair] = act(gate) * up in bfloat16; block == 0: b is [experts, n_out, k], out[pair] float32.
+TK_API int tk_moe_small(const void* a, long long a_stride, int a_div, const void* b, void* out, const int* chosen,
+                        int pairs, int experts, int n_out, int k, int act, int block, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  const size_t smem = (size_t)tk::kMoeSmallRing + (size_t)tk::kMoeSmallRows * k * sizeof(__nv_bfloat16);
+  if (pairs > tk::kMoeSmallMaxPairs || experts < 1 || experts > tk::kMoeMaxExperts || n_out < 1 || k < 8 || k % 8 ||
+      a_stride % 8 || a_div < 1 || block < 0 || (block > 0 && n_out % block) || smem > 200 * 1024 ||
+      ((uintptr_t)a & 15u) || ((uintptr_t)b & 15u)) {
+    return (int)cudaErrorInvalidValue;
+  }
+  tk::MoeSmallParams p;
+  p.a = (const __nv_bfloat16*)a; p.a_stride = a_stride; p.a_div = a_div; p.b = (const __nv_bfloat16*)b; p.out = out;
+  p.chosen = chosen; p.pairs = pairs; p.experts = experts; p.n_out = n_out; p.k = k; p.act = act; p.block = block;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) {
+    return (int)cudaErrorInvalidValue;
+  }
+  cudaError_t e = cudaSuccess;
+  // as many blocks as run at once, and no more than there are rows for the warps of each
+#define TK_MOE_SMALL(G)                                                                                                 \
+  do {                                                                                                                  \
+    e = cudaFuncSetAttribute(tk::moe_small_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+    if (e != cudaSuccess) return (int)e;                                                                                \
+    int per_sm = 0;                                                                                                     \
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tk::moe_small_kernel<G>, tk::kMoeSmallWarps * 32, smem); \
+    if (e != cudaSuccess || per_sm < 1) return (int)(e != cudaSuccess ? e : cudaErrorInvalidValue);                     \
+    const long long most = ((long long)(pairs < experts ? pairs : experts) * n_out + tk::kMoeSmallWarps - 1) /          \
+                           tk::kMoeSmallWarps;                                                                          \
+    const long long blocks = (long long)sms * per_sm < most ? (long long)sms * per_sm : most;                           \
+    e = tk::launch(tk::moe_small_kernel<G>, dim3((unsigned)blocks), dim3(tk::kMoeSmallWarps * 32), smem, stream, p);    \
+  } while (0)
+  if (block > 0) { TK_MOE_SMALL(true); } else { TK_MOE_SMALL(false); }
+#undef TK_MOE_SMALL
+  return (int)e;
 }

@@ -929,6 +929,44 @@ def moe_experts_tc(h: torch.Tensor, routing: MoeRouting, w_gate_up: torch.Tensor
     return out
 
 
+def moe_small_takes(n_tokens: int, top: int, width: int, ff: int) -> bool:
+    """Whether :func:`moe_experts_small` runs a step of these sizes: few enough (token, choice) pairs that an
+    expert's weights are better streamed once past them than multiplied in whole tiles."""
+    return (n_tokens * top <= MOE_SMALL_PAIRS and width % 8 == 0 and ff % 8 == 0 and ff % SWIGLU_TILE_BLOCK == 0
+            and 65536 + 8 * max(width, ff) <= 200 * 1024)
+
+
+def moe_experts_small(h: torch.Tensor, routing: MoeRouting, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                      activation: str = "silu") -> torch.Tensor:
+    """:func:`moe_experts` for steps of few tokens (bfloat16): only the experts that some token chose are
+    read, once, a warp an output row; the sums are float32, the rows between the two products bfloat16.
+    ``w_gate_up`` is what :func:`moe_stack_gate_up` returns.  float32 ``[tokens, width]``."""
+    _want(h, torch.bfloat16, "h"); _want(w_gate_up, torch.bfloat16, "w_gate_up"); _want(w_down, torch.bfloat16, "w_down")
+    n, width = h.shape
+    experts, ff2, _ = w_gate_up.shape
+    ff = ff2 // 2
+    top = routing.chosen.shape[1]
+    if w_gate_up.shape != (experts, 2 * ff, width) or w_down.shape != (experts, width, ff):
+        raise KernelError("moe_experts_small: the weights must be stacked for these sizes")
+    if not moe_small_takes(n, top, width, ff) or h.stride(1) != 1 or h.stride(0) % 8:
+        raise KernelError("moe_experts_small does not take these sizes")
+    if activation not in GLU_ACTIVATIONS:
+        raise KernelError(f"unknown activation {activation!r}")
+    flush_chains()
+    lib, pairs = _lib(), n * top
+    act = torch.empty((pairs, ff), dtype=torch.bfloat16, device=h.device)
+    y = torch.empty((pairs, width), dtype=torch.float32, device=h.device)
+    out = torch.empty((n, width), dtype=torch.float32, device=h.device)
+    _check(lib.tk_moe_small(h.data_ptr(), h.stride(0), top, w_gate_up.data_ptr(), act.data_ptr(),
+                            routing.chosen.data_ptr(), pairs, experts, ff, width, GLU_ACTIVATIONS[activation],
+                            SWIGLU_TILE_BLOCK, _stream()), "moe_small (gate, up)")
+    _check(lib.tk_moe_small(act.data_ptr(), ff, 1, w_down.data_ptr(), y.data_ptr(), routing.chosen.data_ptr(), pairs,
+                            experts, width, ff, 0, 0, _stream()), "moe_small (down)")
+    _check(lib.tk_moe_combine(y.data_ptr(), routing.weights.data_ptr(), out.data_ptr(), n, width, top, _stream()),
+           "moe_combine")
+    return out
+
+
 def moe_experts(h: torch.Tensor, routing: MoeRouting, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
                 activation: str = "silu") -> torch.Tensor:
     """The weighted sum of the chosen experts' gated units, float32 ``[tokens, width]``.  ``w_gate`` and
@@ -1484,6 +1522,11 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
 
 
 SWIGLU_TILE_BLOCK = 64     # gate/up rows alternate in blocks of this many for the fused activation
+# Most (token, choice) pairs of a step whose experts are streamed by the CUDA cores (the kernel takes up to 64).
+# Measured at 8 experts of 4,096 x 2,048, two per token: 1 token 31 us against 65 us on the tensor cores'
+# padded tiles, 4 tokens 87 against 125, 8 tokens 147 against 152, 16 tokens 281 against 157: a pair costs the
+# CUDA cores as much arithmetic as the weights cost to fetch, from about three pairs an expert on.
+MOE_SMALL_PAIRS = 8
 
 
 def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int,

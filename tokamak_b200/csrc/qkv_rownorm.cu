@@ -35,6 +35,14 @@ __global__ void qkv_rownorm_kernel(QkvRowNormParams p) {
   const int t = blockIdx.x;
   const int nq = p.n_q_heads * p.k_dim, nk = p.n_kv_heads * p.k_dim, nv = p.n_kv_heads * p.v_dim;
   const size_t base = (size_t)t * p.in.row_stride;
+  // where the token's keys and values go: a chain of dependent loads, started before the rows are read so
+  // that it is over when the rows are
+  const int pos = p.positions[t], r = p.tok_req[t];
+  const bool known = pos >= 0 && r >= 0 && r < p.n_reqs;
+  const int pidx = known ? pos / p.page_size : 0, slot = known ? pos - pidx * p.page_size : 0;
+  const int page = (known && pidx < p.max_pages) ? p.block_table[(size_t)p.req_slot[r] * p.max_pages + pidx] : -1;
+  int kv_len = 0, q_len = 0;
+  if (known && p.req_kv_len != nullptr) { kv_len = p.req_kv_len[r]; q_len = p.req_q_len[r]; }
   float ssq = 0.0f, ssk = 0.0f;
   for (int c = threadIdx.x; c < nq; c += blockDim.x) {
     const float x = stacked_ld<T>(p.in, base + p.q_off + c) + (p.q_bias ? p.q_bias[c] : 0.0f);
@@ -51,17 +59,13 @@ __global__ void qkv_rownorm_kernel(QkvRowNormParams p) {
   T* q = (T*)p.q_out + (size_t)t * nq;
   for (int c = threadIdx.x; c < nq; c += blockDim.x) q[c] = from_f32<T>(row[c] * rq * (p.q_norm ? p.q_norm[c] : 1.0f));
 
-  const int pos = p.positions[t], r = p.tok_req[t];
   if (pos < 0) { if (threadIdx.x == 0) set_error(p.err, kErrPosition, t, pos, 0); return; }
   if (r < 0 || r >= p.n_reqs) { if (threadIdx.x == 0) set_error(p.err, kErrRequest, t, r, p.n_reqs); return; }
-  const int pidx = pos / p.page_size, slot = pos - pidx * p.page_size;
-  const int page = (pidx < p.max_pages) ? p.block_table[(size_t)p.req_slot[r] * p.max_pages + pidx] : -1;
   if (page < 0 || page >= p.num_pages) { if (threadIdx.x == 0) set_error(p.err, kErrPage, t, pidx, page); return; }
   // the request's last token of this step clears the rest of a page that was begun in this step, so
   // that a live page never holds stale values behind the last position
   int zero_rows = 0;
   if (p.req_kv_len != nullptr) {
-    const int kv_len = p.req_kv_len[r], q_len = p.req_q_len[r];
     if (pos == kv_len - 1 && pos - slot >= kv_len - q_len) zero_rows = p.page_size - 1 - slot;
   }
   for (int c = threadIdx.x; c < nk; c += blockDim.x) {

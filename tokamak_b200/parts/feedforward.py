@@ -190,7 +190,9 @@ class MixtureOfExperts:
         tc = self.w_gate_up is not None
         routing = ops.moe_route(h, self.router, self.correction, top=spec.top, n_groups=spec.num_groups,
                                 keep=spec.keep_groups, padded=tc)
-        if tc:
+        if tc and ops.moe_small_takes(h.shape[0], spec.top, spec.hidden_size, spec.intermediate_size):
+            out = ops.moe_experts_small(h, routing, self.w_gate_up, self.w_down, activation=spec.activation)
+        elif tc:
             out = ops.moe_experts_tc(h, routing, self.w_gate_up, self.w_down, step.err, activation=spec.activation)
         else:
             out = ops.moe_experts(h, routing, self.w_gate, self.w_up, self.w_down, activation=spec.activation)
