@@ -230,7 +230,8 @@ TK_API int tk_branch_norm_add(float* resid, const void* branch, const float* par
   }
   cudaError_t e = cudaSuccess;
   if (grouped) {
-    const int threads = hidden >= 1024 ? 256 : 128;
+    // few rows fill few SMs: more threads a row then (a group's sum is a warp's in either shape, the same bits)
+    const int threads = hidden >= 4096 && n_rows <= 64 ? 1024 : hidden >= 2048 && n_rows <= 64 ? 512 : hidden >= 1024 ? 256 : 128;
     const int most = groups_b > groups_n ? groups_b : groups_n;
     const size_t smem = (size_t)(hidden + most) * sizeof(float);
     if (smem > 96 * 1024) return (int)cudaErrorInvalidValue;

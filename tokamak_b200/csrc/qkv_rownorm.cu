@@ -106,13 +106,15 @@ TK_API int tk_qkv_rownorm(const void* x, const float* parts, int n_parts, long l
   p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.k_dim = k_dim;
   p.v_dim = v_dim; p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages; p.eps = eps;
   cudaError_t e = cudaSuccess;
+  // a step of few tokens fills few SMs: more threads a row then, so that a row is one round of loads
+  const int threads = n_tokens <= 64 ? 1024 : 256;
 #define TK_ROWNORM(T)                                                                                                   \
   do {                                                                                                                  \
     if (smem > 48 * 1024) {                                                                                             \
       e = cudaFuncSetAttribute(tk::qkv_rownorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
       if (e != cudaSuccess) return (int)e;                                                                              \
     }                                                                                                                   \
-    e = tk::launch(tk::qkv_rownorm_kernel<T>, dim3((unsigned)n_tokens), dim3(256), smem, stream, p);                    \
+    e = tk::launch(tk::qkv_rownorm_kernel<T>, dim3((unsigned)n_tokens), dim3(threads), smem, stream, p);                \
   } while (0)
   if (dtype == tk::kF32) { TK_ROWNORM(float); } else if (dtype == tk::kBF16) { TK_ROWNORM(__nv_bfloat16); }
   else return (int)cudaErrorInvalidValue;

@@ -337,13 +337,15 @@ TK_API int tk_ssd_out(const float* o, const float* xbc, int xbc_stride, const vo
   }
   const size_t smem = (size_t)(inner + norm_groups) * sizeof(float);
   cudaError_t e = cudaSuccess;
+  // few tokens fill few SMs: more threads a row then (a group's sum is a warp's in either shape, the same bits)
+  const int threads = n_tokens <= 64 && heads * dv >= 2048 ? 1024 : 256;
 #define TK_SSD_OUT(T)                                                                                                  \
   do {                                                                                                                 \
     if (smem > 48 * 1024) {                                                                                            \
       e = cudaFuncSetAttribute(tk::ssd_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
       if (e != cudaSuccess) return (int)e;                                                                             \
     }                                                                                                                  \
-    e = tk::launch(tk::ssd_out_kernel<T>, dim3((unsigned)n_tokens), dim3(256), smem, stream, o, xbc, xbc_stride,       \
+    e = tk::launch(tk::ssd_out_kernel<T>, dim3((unsigned)n_tokens), dim3(threads), smem, stream, o, xbc, xbc_stride,   \
                    stacked(x, parts, n_parts, part_stride, row_stride), z_off, skip, w, (T*)y, y_stride, heads, dv,    \
                    norm_groups, eps, out_scale);                                                                       \
   } while (0)
