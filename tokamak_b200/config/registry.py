@@ -145,3 +145,7 @@ def _load_builtin() -> None:
     if "Tarivik" not in _ARCHITECTURES:
         from ..models import tarivik
         register_architecture(Architecture(tarivik.ARCHITECTURE, tarivik.parse_config, tarivik.model_spec))
+    if "Pukinex" not in _ARCHITECTURES:
+        from ..models import pukinex
+        register_architecture(Architecture(pukinex.ARCHITECTURE, pukinex.parse_config, pukinex.model_spec,
+                                           reads_tensor_shapes=True))

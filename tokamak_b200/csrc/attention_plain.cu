@@ -18,7 +18,9 @@
 // leading elements of the key rows (a latent cache) are read from the key pages.  Two more: a chunked
 // mask (chunk > 0: a query sees only the keys of its own block of `chunk` positions, blocks counted from
 // position 0 of the sequence) and a distance bias (slopes: one float per query head; the score of key j
-// for the query at position p loses slope * (p - j), after scale and cap).
+// for the query at position p loses slope * (p - j), after scale and cap).  Or a distance bias from a table
+// (dist_bias: [n_q_heads, dist_len] float32): the key at distance n = p - j gains dist_bias[h, min(n, dist_len - 1)],
+// after scale and cap (a learned bias by bucketed distance, the buckets laid out distance by distance).
 #include "common.cuh"
 
 namespace tk {
@@ -32,6 +34,8 @@ struct AttnParams {
   const void* v_cache;      // [num_pages, n_kv_heads, page_size, v_stride]: a row's first v_dim elements
   const float* sinks;       // [n_q_heads] or null
   const float* slopes;      // [n_q_heads] or null
+  const float* dist_bias;   // [n_q_heads, dist_len] or null
+  int dist_len;
   const int* positions;     // [n_tokens]
   const int* tok_req;       // [n_tokens]
   const int* req_slot;      // [n_reqs]
@@ -73,6 +77,7 @@ __global__ void attention_plain_kernel(AttnParams p) {
   int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
   if (p.chunk > 0) lo = max(lo, pos - pos % p.chunk);
   const float slope = p.slopes != nullptr ? p.slopes[hq] : 0.0f;
+  const float* dist = p.dist_bias != nullptr ? p.dist_bias + (size_t)hq * p.dist_len : nullptr;
 
   const TQ* qrow = (const TQ*)p.q + (size_t)t * p.q_tok_stride + (size_t)hq * p.q_head_stride;
   float qreg[kPlainMaxPerLane];
@@ -107,6 +112,7 @@ __global__ void attention_plain_kernel(AttnParams p) {
     dot = warp_sum(dot);
     if (p.softcap > 0.0f) dot = p.softcap * tanhf(dot * inv_cap);
     dot -= slope * (float)(pos - j);
+    if (dist != nullptr) dot += dist[min(pos - j, p.dist_len - 1)];
     const float m_new = fmaxf(m, dot);
     const float corr = expf(m - m_new);   // m = -inf on the first key: exp(-inf) = 0
     const float pj = expf(dot - m_new);
@@ -159,12 +165,13 @@ TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, con
                               int max_pages, int num_pages, int window, float scale, int dtype,
                               int v_dim, float softcap, const float* sinks, int q_dtype, long long q_tok_stride,
                               long long q_head_stride, int k_stride, int v_stride, int chunk, const float* slopes,
-                              cudaStream_t stream) {
+                              const float* dist_bias, int dist_len, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (v_dim <= 0) v_dim = head_dim;
   const int widest = head_dim > v_dim ? head_dim : v_dim;
   if (head_dim < 1 || widest > 1024 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || n_q_heads > 65535 ||
-      k_stride < head_dim || v_stride < v_dim || (q_dtype != dtype && q_dtype != tk::kF32)) {
+      k_stride < head_dim || v_stride < v_dim || (q_dtype != dtype && q_dtype != tk::kF32) ||
+      (dist_bias != nullptr && dist_len < 1)) {
     return (int)cudaErrorInvalidValue;
   }
   tk::AttnParams p;
@@ -173,7 +180,7 @@ TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, con
   p.items = items; p.err = err; p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads;
   p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
   p.max_pages = max_pages; p.num_pages = num_pages; p.window = window; p.scale = scale;
-  p.v_dim = v_dim; p.softcap = softcap; p.sinks = sinks; p.chunk = chunk; p.slopes = slopes;
+  p.v_dim = v_dim; p.softcap = softcap; p.sinks = sinks; p.chunk = chunk; p.slopes = slopes; p.dist_bias = dist_bias; p.dist_len = dist_len;
   p.q_tok_stride = q_tok_stride; p.q_head_stride = q_head_stride; p.k_stride = k_stride; p.v_stride = v_stride;
   dim3 grid(n_tokens, n_q_heads);
   cudaError_t e = cudaSuccess;

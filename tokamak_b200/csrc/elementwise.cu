@@ -232,6 +232,26 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, const float* __restr
   }
 }
 
+// Ungated feed-forward activations, out[t, j] = act(x[t, j]): 0 = silu, 1 = the tanh form of gelu, 2 = relu(x)^2.
+// x may be the float32 partial sums of a split-K product.
+__device__ __forceinline__ float unary_act(float z, int act) {
+  if (act == 2) { const float r = fmaxf(z, 0.0f); return r * r; }
+  return glu_act(z, act);
+}
+
+template <typename T>
+__global__ void unary_act_kernel(const T* __restrict__ x, const float* __restrict__ parts, int n_parts,
+                                 size_t part_stride, T* __restrict__ out, size_t total, int act) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float z;
+    if (parts == nullptr) z = to_f32<T>(x[i]);
+    else { z = 0.0f; for (int s = 0; s < n_parts; ++s) z += parts[(size_t)s * part_stride + i]; }
+    out[i] = from_f32<T>(unary_act(z, act));
+  }
+}
+
 }  // namespace tk
 
 TK_TIMELINE_SETTER(elementwise)
@@ -302,5 +322,18 @@ TK_API int tk_swiglu(const void* gate_up, const float* parts, int n_parts, long 
                     e = tk::launch(tk::swiglu_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, stream,
                                    (const T*)gate_up, parts, n_parts, (size_t)part_stride, (T*)out, inter,
                                    block, total, act));
+  return (int)e;
+}
+
+TK_API int tk_unary_act(const void* x, const float* parts, int n_parts, long long part_stride, void* out,
+                        long long total, int dtype, int act, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if ((x == nullptr) == (parts == nullptr) || act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+  size_t blocks = ((size_t)total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cudaError_t e = cudaSuccess;
+  TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::unary_act_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream,
+                                             (const T*)x, parts, n_parts, (size_t)part_stride, (T*)out, (size_t)total,
+                                             act));
   return (int)e;
 }

@@ -349,10 +349,12 @@ __global__ void __launch_bounds__((kGlaMaxWarps + kGlaService) * 32, 1) gla_scan
   }
 }
 
-// y[t, h, e] = o[t, h, e] * rsqrt(mean_e o^2 + eps) * w[e] * silu(g[t, h, e]);   one warp per (token, head)
+// y[t, h, e] = o[t, h, e] * rsqrt(mean_e o^2 + eps) * w[e] * silu(g[t, h, e]) * out_scale;   one warp per (token, head);
+// rows of y are y_stride elements apart (a column range of wider rows)
 template <typename T>
 __global__ void gla_out_kernel(const float* __restrict__ o, GlaInput in, int g_off, const float* __restrict__ w,
-                               T* __restrict__ y, int n_tokens, int heads, int dv, float eps) {
+                               T* __restrict__ y, int y_stride, float out_scale, int n_tokens, int heads, int dv,
+                               float eps) {
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -371,7 +373,7 @@ __global__ void gla_out_kernel(const float* __restrict__ o, GlaInput in, int g_o
       const float g = gla_ld<T>(in, (size_t)t * in.row_stride + g_off + h * dv + e);
       v *= g / (1.0f + expf(-g));
     }
-    y[(size_t)item * dv + e] = from_f32<T>(v);
+    y[(size_t)t * y_stride + h * dv + e] = from_f32<T>(v * out_scale);
   }
 }
 
@@ -464,8 +466,8 @@ TK_API int tk_gla_scan(const float* prep, float* state, float* out, const int* r
 }
 
 TK_API int tk_gla_out(const float* o, const void* x, const float* parts, int n_parts, int row_stride, int g_off,
-                      const float* w, void* y, int n_tokens, int heads, int value_dim, float eps, int dtype,
-                      cudaStream_t stream) {
+                      const float* w, void* y, int y_stride, float out_scale, int n_tokens, int heads, int value_dim,
+                      float eps, int dtype, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (heads < 1 || value_dim < 1 || (g_off >= 0 && (x == nullptr) == (parts == nullptr))) return (int)cudaErrorInvalidValue;
   const tk::GlaInput in = gla_input(x, parts, n_parts, n_tokens, row_stride);
@@ -473,6 +475,6 @@ TK_API int tk_gla_out(const float* o, const void* x, const float* parts, int n_p
   cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,
                     e = tk::launch(tk::gla_out_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, o, in,
-                                   g_off, w, (T*)y, n_tokens, heads, value_dim, eps));
+                                   g_off, w, (T*)y, y_stride, out_scale, n_tokens, heads, value_dim, eps));
   return (int)e;
 }

@@ -36,7 +36,7 @@ _SIGNATURES: dict[str, list] = {
     "tk_attention_plain": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_float, c_int, c_int, c_float, _P, c_int, c_longlong, c_longlong, c_int, c_int, c_int, _P,
-                           _P],
+                           _P, c_int, _P],
     "tk_latent_prepare": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                           _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
@@ -66,7 +66,16 @@ _SIGNATURES: dict[str, list] = {
                        c_int, _P],
     "tk_ssd_out": [_P, _P, c_int, _P, _P, c_int, c_longlong, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
                    c_int, c_float, c_float, c_int, _P],
-    "tk_gate_scale": [_P, _P, _P, c_int, c_longlong, c_int, c_int, _P, c_int, c_int, c_int, c_float, c_int, _P],
+    "tk_gate_scale": [_P, _P, _P, c_int, c_longlong, c_int, c_int, _P, c_int, c_int, c_int, c_float, c_int, c_int, _P],
+    "tk_retention_prepare": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_float,
+                             c_float, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "tk_qkv_heads": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_float,
+                     _P, c_int, c_int, c_float, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "tk_hyper_mix_norm": [_P, _P, _P, c_int, c_longlong, c_int, _P, _P, _P, _P, _P, _P, _P, _P,
+                          c_int, c_int, c_int, c_int, c_float, c_float, c_int, _P],
+    "tk_logits_scale_cap": [_P, c_longlong, c_float, c_float, _P],
+    "tk_unary_act": [_P, _P, c_int, c_longlong, _P, c_longlong, c_int, c_int, _P],
     "tk_qkv_rownorm": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P,
                        _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                        c_float, c_int, _P],
@@ -85,7 +94,7 @@ _SIGNATURES: dict[str, list] = {
     "tk_gla_prepare": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
                        c_float, c_float, c_int, _P],
     "tk_gla_scan": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
-    "tk_gla_out": [_P, _P, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_float, c_int, _P],
+    "tk_gla_out": [_P, _P, _P, c_int, c_int, c_int, _P, _P, c_int, c_float, c_int, c_int, c_int, c_float, c_int, _P],
     "tk_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, c_float, _P, c_int, _P, _P],

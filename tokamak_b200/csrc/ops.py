@@ -345,7 +345,8 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
                     block_table: torch.Tensor, err: torch.Tensor, *, scale: float,
                     window: int | None = None, items: torch.Tensor | None = None,
                     softcap: float | None = None, sinks: torch.Tensor | None = None,
-                    chunk: int | None = None, slopes: torch.Tensor | None = None) -> None:
+                    chunk: int | None = None, slopes: torch.Tensor | None = None,
+                    dist_bias: torch.Tensor | None = None) -> None:
     """Paged attention of a mixed batch; q is [N, Hq, d], out [N, Hq, dv] with dv the size of a
     value head (``v_cache`` is ``[pages, Hkv, page, dv]``).
 
@@ -356,8 +357,13 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     (``cap * tanh(score / cap)``); ``sinks`` is one float32 per query head whose exponential joins
     the softmax denominator.  ``chunk``: a query sees only the keys of its own block of ``chunk``
     positions (blocks counted from position 0).  ``slopes`` (float32, one per query head): the score of
-    the key at distance ``n`` behind the query loses ``slope * n``."""
+    the key at distance ``n`` behind the query loses ``slope * n``.  ``dist_bias`` (float32 ``[Hq, L]``): the score
+    of the key at distance ``n`` gains ``dist_bias[h, min(n, L - 1)]``."""
     _want(out, k_cache.dtype, "out"); _want(k_cache, None, "k_cache")
+    if dist_bias is not None:
+        _want(dist_bias, torch.float32, "dist_bias")
+        if dist_bias.dim() != 2 or dist_bias.shape[0] != q.shape[1] or dist_bias.shape[1] < 1:
+            raise KernelError("the distance bias must be [query heads, distances]")
     if slopes is not None:
         _want(slopes, torch.float32, "slopes")
         if slopes.numel() != q.shape[1]:
@@ -389,7 +395,8 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
                                         block_table.shape[1], num_pages, int(window or 0),
                                         float(scale), dtype_code(k_cache.dtype), dv, float(softcap or 0.0),
                                         _ptr(sinks), dtype_code(q.dtype), q.stride(0), q.stride(1), d, v_stride,
-                                        int(chunk or 0), _ptr(slopes), _stream()),
+                                        int(chunk or 0), _ptr(slopes), _ptr(dist_bias),
+                                        dist_bias.shape[1] if dist_bias is not None else 0, _stream()),
            "attention_plain")
 
 
@@ -619,9 +626,11 @@ def gla_scan(prep: torch.Tensor, state: torch.Tensor, req_q_start: torch.Tensor,
 
 
 def gla_out(o: torch.Tensor, proj: torch.Tensor | None, g_off: int, weight: torch.Tensor | None, eps: float,
-            dtype: torch.dtype) -> torch.Tensor:
-    """``rmsnorm(o) * weight * silu(gate)`` per (token, head) in the activation type
-    ``[tokens, heads * value_dim]``; the gate is read from ``proj`` at column ``g_off`` (``proj=None``: no gate)."""
+            dtype: torch.dtype, out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor:
+    """``rmsnorm(o) * weight * silu(gate) * out_scale`` per (token, head) in the activation type
+    ``[tokens, heads * value_dim]``; the gate is read from ``proj`` at column ``g_off`` (``proj=None``: no gate);
+    ``weight=None``: the heads are only divided by their root mean square.  ``out`` may be a column range of
+    wider rows."""
     _want(o, torch.float32, "o")
     n, heads, dv = o.shape
     x = parts = None
@@ -636,9 +645,12 @@ def gla_out(o: torch.Tensor, proj: torch.Tensor | None, g_off: int, weight: torc
         _want(weight, torch.float32, "weight")
         if weight.numel() != dv:
             raise KernelError("the norm weight does not match the value size")
-    y = torch.empty((n, heads * dv), dtype=dtype, device=o.device)
+    y = out if out is not None else torch.empty((n, heads * dv), dtype=dtype, device=o.device)
+    if y.dtype != dtype or y.shape != (n, heads * dv) or y.stride(1) != 1:
+        raise KernelError("out must be [tokens, heads * value_dim] in the activation type with dense rows")
     _check(_lib().tk_gla_out(o.data_ptr(), _ptr(x), _ptr(parts), n_parts, row, g_off, _ptr(weight), y.data_ptr(),
-                                n, heads, dv, float(eps), dtype_code(dtype), _stream()), "gla_out")
+                                y.stride(0), float(out_scale), n, heads, dv, float(eps), dtype_code(dtype), _stream()),
+           "gla_out")
     return y
 
 
@@ -783,18 +795,20 @@ def ssd_out(o: torch.Tensor, xbc: torch.Tensor, proj: torch.Tensor, z_off: int, 
 
 
 def gate_scale(x: torch.Tensor, proj: torch.Tensor, g_off: int, out: torch.Tensor | None = None,
-               scale: float = 1.0) -> torch.Tensor:
+               scale: float = 1.0, gate_group: int = 1) -> torch.Tensor:
     """``x * sigmoid(gate) * scale`` with the gate read from ``proj`` at column ``g_off``; ``out`` may be a
-    column range of wider rows."""
+    column range of wider rows.  ``gate_group`` neighbouring columns of ``x`` share one gate column (a gate per
+    head: the head's size)."""
     _want(x, None, "x")
     n, cols = x.shape
     g, parts, n_parts, part_stride, row, n2 = _stacked_args(proj, x.dtype, "proj")
-    if n2 != n or g_off < 0 or g_off + cols > row:
+    if gate_group < 1 or n2 != n or g_off < 0 or g_off + -(-cols // gate_group) > row:
         raise KernelError("the gate columns lie outside the row")
     if out is None:
         out = torch.empty_like(x)
     _check(_lib().tk_gate_scale(x.data_ptr(), g, parts, n_parts, part_stride, row, g_off, out.data_ptr(),
-                                   out.stride(0), n, cols, float(scale), dtype_code(x.dtype), _stream()), "gate_scale")
+                                   out.stride(0), n, cols, float(scale), int(gate_group), dtype_code(x.dtype), _stream()),
+           "gate_scale")
     return out
 
 
@@ -825,6 +839,159 @@ def qkv_rownorm(proj: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, 
                                     step.req_kv_len.data_ptr(), step.err.data_ptr(), n, step.req_slot.numel(), hq, hkv,
                                     d, dv, page_size, block_table.shape[1], num_pages, float(eps),
                                     dtype_code(q_out.dtype), _stream()), "qkv_rownorm")
+
+
+UNARY_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+
+
+def unary_act(x: torch.Tensor, dtype: torch.dtype, activation: str) -> torch.Tensor:
+    """``act(x)`` element by element in the activation type: ``silu``, ``gelu_tanh`` or ``relu2`` (the square of
+    relu).  ``x`` is ``[tokens, cols]`` in ``dtype`` or the float32 partial sums of a split product."""
+    if activation not in UNARY_ACTIVATIONS:
+        raise KernelError(f"unknown activation {activation!r}; known: {', '.join(UNARY_ACTIVATIONS)}")
+    xp, parts, n_parts, n, cols = _parts_of(x, dtype, "x")
+    out = torch.empty((n, cols), dtype=dtype, device=x.device)
+    _check(_lib().tk_unary_act(_ptr(xp), _ptr(parts), n_parts, parts.stride(0) if parts is not None else 0,
+                                  out.data_ptr(), n * cols, dtype_code(dtype), UNARY_ACTIVATIONS[activation], _stream()),
+           "unary_act")
+    return out
+
+
+def logits_scale_cap(logits: torch.Tensor, scale: float = 1.0, cap: float | None = None) -> torch.Tensor:
+    """``cap * tanh(scale * logits / cap)`` in place on float32 logits (``cap=None``: only the scale)."""
+    _want(logits, torch.float32, "logits")
+    _check(_lib().tk_logits_scale_cap(logits.data_ptr(), logits.numel(), float(scale), float(cap or 0.0), _stream()),
+           "logits_scale_cap")
+    return logits
+
+
+HYPER_MAX_STREAMS = 8
+
+
+def hyper_mix_norm(streams: torch.Tensor, branch: torch.Tensor | None, *, mix: torch.Tensor | None = None,
+                   write: torch.Tensor | None = None, read: torch.Tensor | None = None, mult: float = 1.0,
+                   norm_w: torch.Tensor | None = None, norm_b: torch.Tensor | None = None, eps: float = 0.0,
+                   dtype: torch.dtype | None = None, rows: torch.Tensor | None = None,
+                   want_sum: bool = False):
+    """A residual stream in ``S`` float32 copies ``[S, tokens, width]``: the pending sublayer output ``branch``
+    (activation type or float32 partial sums; ``None``: nothing pending) is written to all copies,
+    ``x_t <- sum_s mix[s, t] x_s + mult * write[t] * branch``, then the row ``u = sum_s read[s] x_s`` is read and, with
+    ``norm_w``, layer-normed (``norm_b`` optional) into a new ``[rows, width]`` tensor of ``dtype``.  ``mix``, ``write``
+    and ``read`` default to the identity and ones.  With ``rows`` (int32) only those rows are read and the copies
+    stay as they are.  Returns ``(normed rows | None, u float32 | None)``; ``u`` only with ``want_sum``."""
+    _want(streams, torch.float32, "streams")
+    if streams.dim() != 3 or streams.shape[0] > HYPER_MAX_STREAMS:
+        raise KernelError(f"the stream must be [copies <= {HYPER_MAX_STREAMS}, tokens, width]")
+    S, n, width = streams.shape
+    b = parts = None
+    n_parts = part_stride = row = 0
+    if branch is not None:
+        like = dtype if dtype is not None else (branch.dtype if branch.dim() == 2 else torch.float32)
+        b, parts, n_parts, n2, row = _parts_of(branch, like, "branch")
+        if n2 != n or row != width:
+            raise KernelError("branch and stream differ in shape")
+        part_stride = parts.stride(0) if parts is not None else 0
+        dtype = like
+    for name, t, size in (("mix", mix, S * S), ("write", write, S), ("read", read, S), ("norm_w", norm_w, width),
+                          ("norm_b", norm_b, width)):
+        if t is not None:
+            _want(t, torch.float32, name)
+            if t.numel() != size:
+                raise KernelError(f"{name} has {t.numel()} elements, not {size}")
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+    n_rows = rows.numel() if rows is not None else n
+    out = u = None
+    if norm_w is not None:
+        if dtype is None:
+            raise KernelError("the normed rows need an element type")
+        out = torch.empty((n_rows, width), dtype=dtype, device=streams.device)
+    if want_sum:
+        u = torch.empty((n_rows, width), dtype=torch.float32, device=streams.device)
+    if out is None and u is None and (branch is None or rows is not None):
+        return None, None
+    _check(_lib().tk_hyper_mix_norm(streams.data_ptr(), _ptr(b), _ptr(parts), n_parts, part_stride, row, _ptr(mix),
+                                       _ptr(write), _ptr(read), _ptr(norm_w), _ptr(norm_b), _ptr(out), _ptr(u),
+                                       _ptr(rows), n_rows, n, width, S, float(mult), float(eps),
+                                       dtype_code(dtype if dtype is not None else torch.float32), _stream()),
+           "hyper_mix_norm")
+    return out, u
+
+
+def qkv_heads(proj: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step,
+              block_table: torch.Tensor, *, q_off: int, k_off: int, v_off: int | None, q_bias=None, k_bias=None,
+              v_bias=None, head_norm_eps: float | None = None, q_norm=None, k_norm=None, table=None,
+              rotary_dim: int = 0, halves: bool = False, temp_coef: float = 0.0, temp_every: int = 0) -> None:
+    """Queries, keys and values head by head from the columns of a stacked projection (activation type or
+    float32 partial sums): biases, an RMS norm of every q and k head (``head_norm_eps``; ``q_norm`` / ``k_norm``: a
+    weight of one head's size shared by all heads, or none), the query temperature
+    ``1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)``, rotation over the first ``rotary_dim`` elements of the q
+    and k heads by ``table`` (``[tokens, rotary_dim / 2, 2]`` float32; neighbouring pairs, or ``halves``); queries
+    to ``q_out`` ``[tokens, Hq, d]``, keys and values into their pages.  ``v_off=None``: the values are the key
+    projection as it was before norm and rotation."""
+    n, hq, d = q_out.shape
+    num_pages, hkv, page_size, dk = k_cache.shape
+    dv = v_cache.shape[3]
+    if dk != d or not q_out.is_contiguous() or v_cache.shape[:3] != k_cache.shape[:3]:
+        raise KernelError("qkv_heads shape mismatch")
+    if max(d, dv) > 512:
+        raise KernelError(f"head sizes {d} / {dv} are beyond the kernel's limit of 512")
+    for name, t, size in (("q_bias", q_bias, hq * d), ("k_bias", k_bias, hkv * d), ("v_bias", v_bias, hkv * dv),
+                          ("q_norm", q_norm, d), ("k_norm", k_norm, d)):
+        if t is not None:
+            _want(t, torch.float32, name)
+            if t.numel() != size:
+                raise KernelError(f"{name} does not match the projection")
+    x, parts, n_parts, part_stride, row, n2 = _stacked_args(proj, q_out.dtype, "proj")
+    if n2 != n:
+        raise KernelError("proj and q_out differ in tokens")
+    if v_off is None and dv != d:
+        raise KernelError("values that are the keys have the keys' size")
+    spans = [(q_off, hq * d), (k_off, hkv * d)] + ([(v_off, hkv * dv)] if v_off is not None else [])
+    if any(off < 0 or off + size > row for off, size in spans):
+        raise KernelError("a column range lies outside the row")
+    if table is not None:
+        _want(table, torch.float32, "table")
+        if table.shape != (n, rotary_dim // 2, 2):
+            raise KernelError(f"the rotation table must be [{n}, {rotary_dim // 2}, 2], got {tuple(table.shape)}")
+    elif rotary_dim:
+        raise KernelError("rotary_dim without a rotation table")
+    _check(_lib().tk_qkv_heads(x, parts, n_parts, part_stride, row, q_off, k_off, -1 if v_off is None else v_off,
+                                  _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), _ptr(q_norm), _ptr(k_norm),
+                                  0 if head_norm_eps is None else 1, float(head_norm_eps or 0.0), _ptr(table),
+                                  int(rotary_dim), int(bool(halves)), float(temp_coef), int(temp_every),
+                                  q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), step.positions.data_ptr(),
+                                  step.tok_req.data_ptr(), step.req_slot.data_ptr(), block_table.data_ptr(),
+                                  step.req_q_len.data_ptr(), step.req_kv_len.data_ptr(), step.err.data_ptr(), n,
+                                  step.req_slot.numel(), hq, hkv, d, dv, page_size, block_table.shape[1], num_pages,
+                                  dtype_code(q_out.dtype), _stream()), "qkv_heads")
+
+
+def retention_prepare(proj: torch.Tensor, decay: torch.Tensor, table: torch.Tensor | None, *, dtype: torch.dtype,
+                      q_off: int, k_off: int, v_off: int, heads: int, key_dim: int, value_dim: int, rotary_dim: int = 0,
+                      halves: bool = True, q_scale: float = 1.0, k_scale: float = 1.0) -> torch.Tensor:
+    """The inputs of :func:`gla_scan` for retention: q and k rotated over their first ``rotary_dim`` elements by
+    ``table`` (``[tokens, rotary_dim / 2, 2]`` float32; halves or neighbouring pairs), then scaled; every row of head
+    ``h`` decays by ``decay[h]`` (float32 ``[heads]``); v as projected."""
+    _want(decay, torch.float32, "decay")
+    x, parts, n_parts, part_stride, row, n = _stacked_args(proj, dtype, "proj")
+    if decay.numel() != heads:
+        raise KernelError("one decay per head is needed")
+    for off, size in ((q_off, heads * key_dim), (k_off, heads * key_dim), (v_off, heads * value_dim)):
+        if off < 0 or off + size > row:
+            raise KernelError("a column range lies outside the row")
+    if table is not None:
+        _want(table, torch.float32, "table")
+        if table.shape != (n, rotary_dim // 2, 2):
+            raise KernelError(f"the rotation table must be [{n}, {rotary_dim // 2}, 2], got {tuple(table.shape)}")
+    elif rotary_dim:
+        raise KernelError("rotary_dim without a rotation table")
+    prep = _prep_buffer(n, heads, key_dim, value_dim, decay.device)
+    _check(_lib().tk_retention_prepare(x, parts, n_parts, part_stride, row, q_off, k_off, v_off, decay.data_ptr(),
+                                          _ptr(table), int(rotary_dim), int(bool(halves)), float(q_scale),
+                                          float(k_scale), prep.data_ptr(), n, heads, key_dim, value_dim,
+                                          dtype_code(dtype), _stream()), "retention_prepare")
+    return prep
 
 
 def moe_tile_rows() -> int:

@@ -19,6 +19,8 @@
 // * A state-space layer with a scalar decay per head (Mamba-2): dt = softplus(z_dt + dt_bias),
 //   alpha = exp(-exp(A_log) dt) for every row, k = B, q = C (shared by the heads of a group), v = dt x; the
 //   output stage adds D x, multiplies by silu(z) and applies an RMS norm in equal groups with a weight.
+// * Retention: a fixed decay per head and rotated queries and keys: alpha = decay_h for every row,
+//   q and k rotated over their first `rotary_dim` elements (neighbouring pairs or halves), k then scaled.
 #include "common.cuh"
 #include "group_norm.cuh"
 #include "stacked_input.cuh"
@@ -209,6 +211,39 @@ __global__ void ssd_prepare_kernel(const float* __restrict__ xbc, StackedInput i
   prep_qka(l, h, t, e, row[inner + (groups + g) * l.dk + e], row[inner + g * l.dk + e], expf(-expf(a_log[h]) * dt));
 }
 
+// Retention's inputs: q and k rotated by the token's angles (table [tokens, rotary_dim / 2] of (cos, sin)), k times
+// k_scale after the rotation, q times q_scale, alpha = decay[h] on every row of the head.
+template <typename T>
+__global__ void retention_prepare_kernel(StackedInput in, int q_off, int k_off, int v_off, const float* __restrict__ decay,
+                                         const float2* __restrict__ table, int rotary_dim, int halves, float q_scale,
+                                         float k_scale, PrepLayout l) {
+  pdl_trigger();
+  pdl_wait();
+  int t, h, e;
+  if (!prep_item(l, t, h, e)) return;
+  const size_t row = (size_t)t * in.row_stride;
+  if (e >= l.dks) {
+    const int c = e - l.dks;
+    prep_v(l, h, t, c, c < l.dv ? stacked_ld<T>(in, row + v_off + h * l.dv + c) : 0.0f);
+    return;
+  }
+  if (e >= l.dk) { prep_qka(l, h, t, e, 0.0f, 0.0f, 0.0f); return; }
+  const int ch = h * l.dk + e;
+  float q = stacked_ld<T>(in, row + q_off + ch), k = stacked_ld<T>(in, row + k_off + ch);
+  if (table != nullptr && e < rotary_dim) {
+    const int half = rotary_dim >> 1;
+    int partner, idx; bool first;
+    if (halves) { first = e < half; partner = first ? e + half : e - half; idx = first ? e : e - half; }
+    else { first = !(e & 1); partner = e ^ 1; idx = e >> 1; }
+    const float2 cs = table[(size_t)t * half + idx];
+    const float qo = stacked_ld<T>(in, row + q_off + h * l.dk + partner);
+    const float ko = stacked_ld<T>(in, row + k_off + h * l.dk + partner);
+    q = first ? q * cs.x - qo * cs.y : q * cs.x + qo * cs.y;
+    k = first ? k * cs.x - ko * cs.y : k * cs.x + ko * cs.y;
+  }
+  prep_qka(l, h, t, e, q * q_scale, k * k_scale, decay[h]);
+}
+
 // y = norm_groups((o + D x) silu(z)) * w * out_scale; one block per token, the row in shared memory.
 template <typename T>
 __global__ void ssd_out_kernel(const float* __restrict__ o, const float* __restrict__ xbc, int xbc_stride,
@@ -235,13 +270,13 @@ __global__ void ssd_out_kernel(const float* __restrict__ o, const float* __restr
 // y[t, c] = x[t, c] * sigmoid(g[t, g_off + c]) * scale, into rows of their own stride.
 template <typename T>
 __global__ void gate_scale_kernel(const T* __restrict__ x, StackedInput in, int g_off, T* __restrict__ y, int y_stride,
-                                  int n_tokens, int cols, float scale) {
+                                  int n_tokens, int cols, float scale, int gate_group) {
   pdl_trigger();
   pdl_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)n_tokens * cols) return;
   const int t = (int)(idx / cols), c = (int)(idx - (long long)t * cols);
-  const float g = stacked_ld<T>(in, (size_t)t * in.row_stride + g_off + c);
+  const float g = stacked_ld<T>(in, (size_t)t * in.row_stride + g_off + c / gate_group);
   y[(size_t)t * y_stride + c] = from_f32<T>(to_f32<T>(x[idx]) * sigmoidf_(g) * scale);
 }
 
@@ -310,6 +345,23 @@ TK_API int tk_mlstm_out(const float* o, const float* gates, const void* x, const
   return (int)e;
 }
 
+TK_API int tk_retention_prepare(const void* x, const float* parts, int n_parts, long long part_stride, int row_stride,
+                                int q_off, int k_off, int v_off, const float* decay, const float* table, int rotary_dim,
+                                int halves, float q_scale, float k_scale, float* prep, int n_tokens, int heads, int dk,
+                                int dv, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if ((x == nullptr) == (parts == nullptr) || heads < 1 || dk < 1 || dv < 1 || rotary_dim < 0 || rotary_dim > dk ||
+      (rotary_dim & 1) || decay == nullptr) {
+    return (int)cudaErrorInvalidValue;
+  }
+  const tk::PrepLayout l = layout(prep, n_tokens, heads, dk, dv);
+  cudaError_t e = cudaSuccess;
+  TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::retention_prepare_kernel<T>, dim3(prep_blocks(l)), dim3(256), 0, stream,
+                                             stacked(x, parts, n_parts, part_stride, row_stride), q_off, k_off, v_off,
+                                             decay, (const float2*)table, rotary_dim, halves, q_scale, k_scale, l));
+  return (int)e;
+}
+
 TK_API int tk_ssd_prepare(const float* xbc, const void* x, const float* parts, int n_parts, long long part_stride,
                           int row_stride, int dt_off, const float* dt_bias, const float* a_log, float* prep,
                           int n_tokens, int heads, int groups, int dk, int dv, int dtype, cudaStream_t stream) {
@@ -357,13 +409,13 @@ TK_API int tk_ssd_out(const float* o, const float* xbc, int xbc_stride, const vo
 
 TK_API int tk_gate_scale(const void* x, const void* g, const float* g_parts, int n_parts, long long part_stride,
                          int row_stride, int g_off, void* y, int y_stride, int n_tokens, int cols, float scale,
-                         int dtype, cudaStream_t stream) {
+                         int gate_group, int dtype, cudaStream_t stream) {
   if (n_tokens <= 0 || cols <= 0) return 0;
-  if ((g == nullptr) == (g_parts == nullptr)) return (int)cudaErrorInvalidValue;
+  if ((g == nullptr) == (g_parts == nullptr) || gate_group < 1) return (int)cudaErrorInvalidValue;
   const long long total = (long long)n_tokens * cols;
   cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::gate_scale_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256),
                                              0, stream, (const T*)x, stacked(g, g_parts, n_parts, part_stride, row_stride),
-                                             g_off, (T*)y, y_stride, n_tokens, cols, scale));
+                                             g_off, (T*)y, y_stride, n_tokens, cols, scale, gate_group));
   return (int)e;
 }

@@ -29,7 +29,10 @@ class LayerCall:
 class ModelSpec:
     """A model as data.  Every field but the schedule is a spec with a ``kind`` that one of the
     registries of ``parts/base.py`` resolves; ``embedding_position`` is the seat of a position
-    encoding that is added to the embedded rows (``None``: the mixers carry the positions)."""
+    encoding that is added to the embedded rows (``None``: the mixers carry the positions).
+    ``streams > 1``: the residual stream is kept in that many float32 copies ``[streams, tokens, width]``, all
+    equal to the embedded rows at the start; the blocks and the last norm must know such a stream (the
+    ``hyper`` block, the ``layernorm`` norm, which reads the sum of the copies at the end)."""
 
     embedding: object                  # an embedding spec (vocab_size, hidden_size, kind, ...)
     blocks: tuple                      # block specs, each with a unique ``name``
@@ -38,6 +41,7 @@ class ModelSpec:
     final_norm_name: str
     head: object                       # a head spec (vocab_size, kind, ...)
     embedding_position: object = None
+    streams: int = 1
 
     def __post_init__(self) -> None:
         names = [b.name for b in self.blocks]
@@ -137,6 +141,8 @@ class DecoderModel:
         resid = self.embedding.forward(step)
         if self.embedding_position is not None:
             self.embedding_position.add_to_embedding(resid, step)
+        if self.spec.streams > 1:
+            resid = resid.unsqueeze(0).repeat(self.spec.streams, 1, 1)
         pending = None
         schedule = self.spec.schedule
         for i, call in enumerate(schedule):

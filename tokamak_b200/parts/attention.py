@@ -393,6 +393,186 @@ class RowNormAttention:
         return linear(self.branch(h, step, cache_view), self.w_o, err=step.err)
 
 
+def bucketed_distance_table(rel: torch.Tensor, far: int) -> torch.Tensor:
+    """A learned bias by bucketed distance, laid out distance by distance: ``[heads, far + 1]`` float32 with
+    ``out[h, n] = rel[bucket(n), h]``.  ``rel`` has ``B`` rows; distances below ``B / 2`` have a bucket each, the
+    further ones share the rest on a logarithmic scale that reaches the last bucket at ``far``:
+    ``bucket(n) = B/2 + floor(ln(n / (B/2)) / ln(far / (B/2)) * (B - B/2))``, at most ``B - 1``; every distance from
+    ``far`` on has the last bucket, so a reader clamps the distance to the table's last column."""
+    import math
+    rows, heads = rel.shape
+    half = rows // 2
+    if half < 1 or far <= half:
+        raise ValueError(f"{rows} buckets up to distance {far}: the logarithmic part is empty")
+    idx = []
+    for n in range(far + 1):
+        if n < half:
+            idx.append(n)
+        else:
+            idx.append(min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
+    index = torch.tensor(idx, dtype=torch.long, device=rel.device)
+    return rel.float().index_select(0, index).t().contiguous()
+
+
+@dataclass(frozen=True)
+class GatedAttentionSpec:
+    """Sizes and constants of an attention mixer with the options of :class:`GatedAttention`.
+
+    ``bias``: the q, k and v projections have biases.  ``values_from_keys``: there is no value projection; the
+    values are the key projection as it is before norm and rotation.  ``head_norm_eps``: q and k heads are RMS
+    normed, with a weight of one head's size shared by all heads (``head_norm_weight``) or none.  ``position``: a
+    position spec whose part rotates neighbouring pairs or halves, or ``none``.  ``q_temp`` ``(coef, every)``: the
+    query at position ``p`` is multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``.  ``softcap``: scores
+    are bounded by ``cap * tanh(s / cap)``.  ``unit_sink``: one is added to every softmax denominator (a sink of
+    score 0 without a value).  ``rel_far``: a learned bias ``rel[bucket(i - j), h]`` joins the score, see
+    :func:`bucketed_distance_table`; the table's rows are read from the checkpoint.  ``gate``: ``"head"`` (one
+    sigmoid gate per head) or ``"channel"`` (one per output channel) or ``None``.  The ``*_name`` fields are the
+    tensors' names after the part's prefix."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    softmax_scale: float
+    position: object
+    bias: bool = False
+    values_from_keys: bool = False
+    head_norm_eps: float | None = None
+    head_norm_weight: bool = True
+    q_temp: tuple | None = None
+    softcap: float | None = None
+    unit_sink: bool = False
+    rel_far: int | None = None
+    rel_rows: int | None = None
+    gate: str | None = None
+    window: int | None = None
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    o_name: str = "o"
+    gate_name: str = "g"
+    rel_name: str = "rel"
+    bias_suffix: str = ".b"
+    norm_suffix: str = ".norm"
+    kind: str = "attention_gated"
+
+
+@MIXERS.register("attention_gated")
+class GatedAttention:
+    """Grouped-query attention over paged keys and values; query head ``h`` reads key/value head
+    ``h // (Hq / Hkv)``; ``score = (q . k) * scale``, capped, plus the distance bias; causal; the softmax
+    denominator may hold one more term ``exp(0)``; the heads are gated by ``sigmoid(W_g h)`` before the output
+    projection.
+
+    The q, k, v and gate matrices are one stacked operand.  Biases, head norms, the query temperature, the
+    rotation and the page write are one kernel (``csrc/qkv_heads.cu``); scores, cap, bias, softmax and the
+    weighted sum run in float32 inside the attention kernel; gate and the caller's factor are one kernel.
+    :meth:`branch` writes the rows in front of the output projection into a buffer of the caller's (see
+    :class:`~tokamak_b200.parts.parallel.ParallelMixer`)."""
+
+    def __init__(self, spec: GatedAttentionSpec, prefix: str, tensors: dict[str, torch.Tensor], rt: Runtime):
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"{spec.num_heads} query heads are not a multiple of "
+                             f"{spec.num_kv_heads} key/value heads")
+        if max(spec.head_dim, spec.v_head_dim) > 512:
+            raise ValueError(f"head sizes {spec.head_dim} / {spec.v_head_dim} are beyond the kernels' 512")
+        if spec.values_from_keys and spec.v_head_dim != spec.head_dim:
+            raise ValueError("values that are the keys have the keys' size")
+        if spec.gate not in (None, "head", "channel"):
+            raise ValueError(f"gate must be None, 'head' or 'channel', got {spec.gate!r}")
+        self.spec = spec
+        self.rt = rt
+        t = lambda name: tensors[prefix + name]
+        mats = [t(spec.q_name), t(spec.k_name)] + ([] if spec.values_from_keys else [t(spec.v_name)])
+        nq, nk = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        nv = 0 if spec.values_from_keys else spec.num_kv_heads * spec.v_head_dim
+        self.q_off, self.k_off = 0, nq
+        self.v_off = None if spec.values_from_keys else nq + nk
+        self.g_off = nq + nk + nv
+        if spec.gate is not None:
+            mats.append(t(spec.gate_name))
+        self.w_in = torch.cat(mats, dim=0).contiguous()
+        vec = lambda name: t(name).contiguous()
+        self.q_bias = vec(spec.q_name + spec.bias_suffix) if spec.bias else None
+        self.k_bias = vec(spec.k_name + spec.bias_suffix) if spec.bias else None
+        self.v_bias = vec(spec.v_name + spec.bias_suffix) if spec.bias and not spec.values_from_keys else None
+        normed = spec.head_norm_eps is not None and spec.head_norm_weight
+        self.q_norm = vec(spec.q_name + spec.norm_suffix) if normed else None
+        self.k_norm = vec(spec.k_name + spec.norm_suffix) if normed else None
+        self.sinks = torch.zeros(spec.num_heads, dtype=torch.float32, device=rt.device) if spec.unit_sink else None
+        self.dist_bias = bucketed_distance_table(t(spec.rel_name), spec.rel_far) if spec.rel_far is not None else None
+        self.position = POSITIONS.get(spec.position.kind)(spec.position, tensors, rt)
+        if not hasattr(self.position, "rotary_table"):
+            raise ValueError(f"position encoding {spec.position.kind!r} does not rotate queries and keys")
+        self.halves = getattr(self.position, "PAIRING", "halves") == "halves"
+        self.w_o = t(spec.o_name)
+        self.out_width = spec.num_heads * spec.v_head_dim
+        self.prefill_heads = spec.num_heads
+
+    @staticmethod
+    def expected_tensors(spec: GatedAttentionSpec, prefix: str) -> dict[str, TensorReq]:
+        h, d, dv = spec.hidden_size, spec.head_dim, spec.v_head_dim
+        sizes = [(spec.q_name, spec.num_heads * d), (spec.k_name, spec.num_kv_heads * d)]
+        if not spec.values_from_keys:
+            sizes.append((spec.v_name, spec.num_kv_heads * dv))
+        out = {}
+        for name, rows in sizes:
+            out[prefix + name] = TensorReq((rows, h))
+            if spec.bias:
+                out[prefix + name + spec.bias_suffix] = TensorReq((rows,), role="bias")
+        if spec.head_norm_eps is not None and spec.head_norm_weight:
+            out[prefix + spec.q_name + spec.norm_suffix] = TensorReq((d,), role="vector")
+            out[prefix + spec.k_name + spec.norm_suffix] = TensorReq((d,), role="vector")
+        if spec.rel_far is not None:
+            out[prefix + spec.rel_name] = TensorReq((spec.rel_rows, spec.num_heads), role="bias")
+        if spec.gate is not None:
+            out[prefix + spec.gate_name] = TensorReq((spec.num_heads if spec.gate == "head" else spec.num_heads * dv, h))
+        out[prefix + spec.o_name] = TensorReq((h, spec.num_heads * dv))
+        out.update(POSITIONS.get(spec.position.kind).expected_tensors(spec.position))
+        return out
+
+    def cache_need(self) -> KVPagesNeed:
+        s = self.spec
+        return KVPagesNeed(s.num_kv_heads, s.head_dim, s.window, None if s.v_head_dim == s.head_dim else s.v_head_dim)
+
+    def GRAPH_SAFE(self) -> bool:
+        return graph_safe(self.position)
+
+    def weight_bytes(self) -> int:
+        return tensor_bytes(self.w_in, self.w_o, self.q_bias, self.k_bias, self.v_bias, self.q_norm, self.k_norm,
+                            self.dist_bias)
+
+    def branch(self, h, step, cache_view, out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor:
+        spec = self.spec
+        n = h.shape[0]
+        proj = linear(h, self.w_in, err=step.err)
+        q = torch.empty((n, spec.num_heads, spec.head_dim), dtype=h.dtype, device=h.device)
+        table, rotary_dim = self.position.rotary_table(step)
+        coef, every = spec.q_temp if spec.q_temp is not None else (0.0, 0)
+        ops.qkv_heads(proj, q, cache_view.k, cache_view.v, step, cache_view.table, q_off=self.q_off, k_off=self.k_off,
+                      v_off=self.v_off, q_bias=self.q_bias, k_bias=self.k_bias, v_bias=self.v_bias,
+                      head_norm_eps=spec.head_norm_eps, q_norm=self.q_norm, k_norm=self.k_norm, table=table,
+                      rotary_dim=rotary_dim, halves=self.halves, temp_coef=coef, temp_every=every)
+        att = torch.empty((n, spec.num_heads, spec.v_head_dim), dtype=h.dtype, device=h.device)
+        paged_attention(q, att, cache_view, step, scale=spec.softmax_scale, window=spec.window, softcap=spec.softcap,
+                        sinks=self.sinks, dist_bias=self.dist_bias)
+        att = att.view(n, self.out_width)
+        if spec.gate is None:
+            if out is None and out_scale == 1.0:
+                return att
+            res = att.float().mul_(out_scale).to(h.dtype)
+            if out is None:
+                return res
+            out.copy_(res)
+            return out
+        return ops.gate_scale(att, proj, self.g_off, out=out, scale=out_scale,
+                              gate_group=spec.v_head_dim if spec.gate == "head" else 1)
+
+    def forward(self, h, step, cache_view):
+        return linear(self.branch(h, step, cache_view), self.w_o, err=step.err)
+
+
 _SIDE: dict = {}
 
 
@@ -407,14 +587,16 @@ def _side_stream(device: torch.device):
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, scale: float,
                     window: int | None, softcap: float | None = None, sinks: torch.Tensor | None = None,
-                    chunk: int | None = None, slopes: torch.Tensor | None = None) -> None:
+                    chunk: int | None = None, slopes: torch.Tensor | None = None,
+                    dist_bias: torch.Tensor | None = None) -> None:
     """Attention of every token of the step over the pages of its own request.
 
     ``softcap`` bounds the scaled scores by ``cap * tanh(score / cap)``; ``sinks`` (float32, one per
     query head) adds ``exp(sink)`` to every softmax denominator.  ``out`` is ``[N, Hq, dv]`` where
     the value heads have a size of their own.  ``chunk`` (a query sees only its own block of that many
     positions) and ``slopes`` (a distance bias per query head) are known to the general kernel, the decode
-    kernels and the tcgen05 prefill kernel.
+    kernels and the tcgen05 prefill kernel.  ``dist_bias`` (float32 ``[Hq, L]``: the score of the key ``n``
+    positions back gains ``dist_bias[h, min(n, L - 1)]``) is known to the general kernel.
 
     Chooses the kernels.  A latent cache in bfloat16 goes to the tensor-core kernel that stacks the heads
     of a token (``csrc/attention_latent.cu``).  bfloat16 with a head_dim the tiled kernels take: single next
@@ -447,8 +629,9 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     extras = softcap is not None or sinks is not None or chunk is not None or slopes is not None
     # a single token sees no more keys than its chunk holds: the kernels' work is planned for that many
     dec_span = step.max_kv_len if chunk is None else min(step.max_kv_len, chunk)
-    dec_tiled = bf16 and n_dec > 0 and same_size and ops.decode_kernel_takes(hq, hkv, d, page)
-    pf_tiled = (bf16 and n_pf > 0 and same_size and ops.prefill_kernel_takes(hq, hkv, d, page)
+    tiled = bf16 and same_size and dist_bias is None
+    dec_tiled = tiled and n_dec > 0 and ops.decode_kernel_takes(hq, hkv, d, page)
+    pf_tiled = (tiled and n_pf > 0 and ops.prefill_kernel_takes(hq, hkv, d, page)
                 and (not extras or ops.prefill_tc_kernel_takes(hq, hkv, d, page)))
     # In a mixed step the two kernels touch different tokens.  One portion against a long context
     # is few blocks (one per pair of 128-row query tiles and head), so the decode kernel runs
@@ -488,4 +671,5 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
         items = None if (dec_rest and pf_rest) else (step.decode_items if dec_rest else step.prefill_items)
         ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req,
                             step.req_slot, cache_view.table, step.err, scale=scale, window=window,
-                            items=items, softcap=softcap, sinks=sinks, chunk=chunk, slopes=slopes)
+                            items=items, softcap=softcap, sinks=sinks, chunk=chunk, slopes=slopes,
+                            dist_bias=dist_bias)

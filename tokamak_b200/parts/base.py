@@ -200,6 +200,20 @@ class NormedBranch:
 
 
 @dataclass
+class HyperBranch:
+    """A sublayer output that waits to be written to a residual stream kept in several copies:
+    ``x_t <- sum_s mix[s, t] x_s + mult * write[t] * x`` (``mix`` float32 ``[S, S]`` indexed [from, to], ``write``
+    float32 ``[S]``; ``None``: the identity and ones, which with one copy is the plain ``x <- x + mult * branch``).
+    The norm that reads the stream next (:class:`~tokamak_b200.parts.norm.LayerNorm`) does the write, the read
+    and its normalisation in one kernel.  ``x`` is what :func:`linear` returned."""
+
+    x: torch.Tensor
+    mix: torch.Tensor | None = None
+    write: torch.Tensor | None = None
+    mult: float = 1.0
+
+
+@dataclass
 class OwedNorm:
     """Input of a norm whose scaling by the statistic is still owed.
 

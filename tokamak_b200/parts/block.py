@@ -6,8 +6,8 @@ from dataclasses import dataclass
 
 import torch
 
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, NormedBranch, OwedNorm, Runtime, TensorReq, graph_safe,
-                   weight_bytes)
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, HyperBranch, NormedBranch, OwedNorm, Runtime, TensorReq,
+                   graph_safe, weight_bytes)
 
 
 @dataclass(frozen=True)
@@ -257,4 +257,114 @@ class SandwichBlock:
         if self.feed_forward is not None:
             h = self._read(self.norm_in2, self.conv2, views.get("conv2"), resid, pending, step)
             pending = self._leave(self.feed_forward.forward(h, step), self.norm_out2, self.scale2)
+        return resid, pending
+
+
+@dataclass(frozen=True)
+class HyperBlockSpec:
+    """A pre-norm block over a residual stream kept in ``streams`` copies.  Sublayer ``q`` (1: the mixer, 2: the
+    feed-forward, which may be absent) has three tensors under ``hc<q>_prefix``: ``in`` ``[streams]`` (how the copies
+    are read), ``out`` ``[streams]`` (how its output is written to each copy) and ``mix`` ``[streams, streams]``
+    (how the copies are mixed meanwhile, indexed [from, to]).  ``connections=False``: no such tensors; the block
+    is then ``x <- x + mult * sublayer(norm(x))`` on the one copy it is given.  ``mult`` scales what a sublayer
+    adds.  The ``*_name`` fields are full tensor names; the prefixes end with a dot."""
+
+    name: str
+    norm1: object
+    mixer: object
+    norm1_name: str
+    mixer_prefix: str
+    streams: int = 1
+    connections: bool = True
+    mult: float = 1.0
+    norm2: object = None
+    feed_forward: object = None
+    norm2_name: str | None = None
+    ffn_prefix: str | None = None
+    hc1_prefix: str | None = None
+    hc2_prefix: str | None = None
+    in_name: str = "in"
+    out_name: str = "out"
+    mix_name: str = "mix"
+    kind: str = "hyper"
+
+
+@BLOCKS.register("hyper")
+class HyperBlock:
+    """For each sublayer: ``u = sum_s in[s] x_s``, ``y = sublayer(norm(u))``, then, all copies at once from the old
+    ones, ``x_t <- sum_s mix[s, t] x_s + mult * out[t] * y``.
+
+    The write is left pending as a :class:`~tokamak_b200.parts.base.HyperBranch`; the norm in front of the next
+    sublayer (this block's, the next block's, the model's last) does it together with its own read and
+    normalisation, so the copies cross memory once per sublayer.  The norms must take a ``read`` argument
+    (:class:`~tokamak_b200.parts.norm.LayerNorm`)."""
+
+    def __init__(self, spec: HyperBlockSpec, tensors: dict[str, torch.Tensor], rt: Runtime):
+        if spec.streams < 1 or (not spec.connections and spec.streams != 1):
+            raise ValueError(f"{spec.streams} copies of the stream without connections between them")
+        self.spec = spec
+        self.rt = rt
+        self.norm1 = NORMS.get(spec.norm1.kind)(spec.norm1, spec.norm1_name, tensors, rt)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, spec.mixer_prefix, tensors, rt)
+        self.norm2 = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.norm2 = NORMS.get(spec.norm2.kind)(spec.norm2, spec.norm2_name, tensors, rt)
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, spec.ffn_prefix, tensors, rt)
+        self.hc1 = self._connections(spec.hc1_prefix, tensors)
+        self.hc2 = self._connections(spec.hc2_prefix, tensors) if spec.feed_forward is not None else None
+
+    def _connections(self, prefix, tensors):
+        if not self.spec.connections:
+            return None, None, None
+        s = self.spec
+        return tuple(tensors[prefix + n].float().contiguous() for n in (s.in_name, s.out_name, s.mix_name))
+
+    @staticmethod
+    def expected_tensors(spec: HyperBlockSpec) -> dict[str, TensorReq]:
+        out: dict[str, TensorReq] = {}
+        out.update(NORMS.get(spec.norm1.kind).expected_tensors(spec.norm1, spec.norm1_name))
+        out.update(MIXERS.get(spec.mixer.kind).expected_tensors(spec.mixer, spec.mixer_prefix))
+        prefixes = [spec.hc1_prefix]
+        if spec.feed_forward is not None:
+            out.update(NORMS.get(spec.norm2.kind).expected_tensors(spec.norm2, spec.norm2_name))
+            out.update(FEED_FORWARDS.get(spec.feed_forward.kind).expected_tensors(spec.feed_forward, spec.ffn_prefix))
+            prefixes.append(spec.hc2_prefix)
+        if spec.connections:
+            for prefix in prefixes:
+                out[prefix + spec.in_name] = TensorReq((spec.streams,), role="fraction")
+                out[prefix + spec.out_name] = TensorReq((spec.streams,), role="vector")
+                out[prefix + spec.mix_name] = TensorReq((spec.streams, spec.streams), role="fraction")
+        return out
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def _parts(self) -> list:
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    def GRAPH_SAFE(self) -> bool:
+        return graph_safe(*self._parts())
+
+    @property
+    def prefill_heads(self) -> int | None:
+        return getattr(self.mixer, "prefill_heads", None)
+
+    def weight_bytes(self) -> int:
+        return weight_bytes(*self._parts())
+
+    @property
+    def entry_norm(self):
+        return self.norm1
+
+    def forward(self, resid: torch.Tensor, pending, step, cache_view):
+        copies = resid.shape[0] if resid.dim() == 3 else 1
+        if copies != self.spec.streams:
+            raise ValueError(f"the block works on {self.spec.streams} copies of the stream and is given {copies}")
+        read, write, mix = self.hc1
+        h = self.norm1.add_norm(resid, pending, read=read)
+        pending = HyperBranch(self.mixer.forward(h, step, cache_view), mix, write, self.spec.mult)
+        if self.feed_forward is not None:
+            read, write, mix = self.hc2
+            h = self.norm2.add_norm(resid, pending, read=read)
+            pending = HyperBranch(self.feed_forward.forward(h, step), mix, write, self.spec.mult)
         return resid, pending

@@ -29,6 +29,8 @@ class HeadSpec:
     tied: bool
     name: str = "lm_head.weight"
     kind: str = "linear_head"
+    scale: float = 1.0              # the logits are multiplied by it
+    softcap: float | None = None    # and then bounded: cap * tanh(logits / cap)
 
 
 @EMBEDDINGS.register("embedding")
@@ -81,4 +83,9 @@ class Head:
         # queued with the products before it; the model flushes the queue before it returns the logits
         logits = linear(h, self.weight, out_dtype=torch.float32, err=getattr(step, "err", None), chain=chain_of(step),
                         queue_plain=True)
-        return sum_parts(logits, torch.float32)
+        logits = sum_parts(logits, torch.float32)
+        if self.spec.scale != 1.0 or self.spec.softcap is not None:
+            if not logits.is_contiguous():
+                logits = logits.contiguous()
+            ops.logits_scale_cap(logits, self.spec.scale, self.spec.softcap)
+        return logits

@@ -101,6 +101,50 @@ class SwiGLU:
 
 
 @dataclass(frozen=True)
+class MlpSpec:
+    """An ungated unit ``down(act(up(x)))``; ``activation`` is ``relu2`` (the square of relu), ``gelu_tanh`` or
+    ``silu``; the names are the tensors' names after the part's prefix."""
+
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "relu2"
+    up_name: str = "up"
+    down_name: str = "down"
+    kind: str = "mlp"
+
+
+@FEED_FORWARDS.register("mlp")
+class Mlp:
+    """``W_down act(W_up x)`` without biases: a product, the activation (a kernel that also adds up the float32
+    partial sums of a split product, ``csrc/elementwise.cu``), a product."""
+
+    GRAPH_SAFE = True
+
+    def __init__(self, spec: MlpSpec, prefix: str, tensors: dict[str, torch.Tensor], rt: Runtime):
+        if spec.activation not in ops.UNARY_ACTIVATIONS:
+            raise ValueError(f"unknown activation {spec.activation!r}; known: {', '.join(ops.UNARY_ACTIVATIONS)}")
+        self.spec = spec
+        self.rt = rt
+        self.w_up = tensors[prefix + spec.up_name]
+        self.w_down = tensors[prefix + spec.down_name]
+
+    @staticmethod
+    def expected_tensors(spec: MlpSpec, prefix: str) -> dict[str, TensorReq]:
+        h, i = spec.hidden_size, spec.intermediate_size
+        return {prefix + spec.up_name: TensorReq((i, h)), prefix + spec.down_name: TensorReq((h, i))}
+
+    def weight_bytes(self) -> int:
+        return tensor_bytes(self.w_up, self.w_down)
+
+    def forward(self, h, step):
+        err = step.err if step is not None else None
+        if isinstance(h, OwedNorm):
+            h = h.materialize()
+        act = ops.unary_act(linear(h, self.w_up, err=err), h.dtype, self.spec.activation)
+        return linear(act, self.w_down, err=err)
+
+
+@dataclass(frozen=True)
 class MoESpec:
     """A mixture of ``num_experts`` gated units of inner size ``intermediate_size`` of which every token uses
     ``top``.  The experts form ``num_groups`` equal groups of neighbours and only experts of the ``keep_groups``

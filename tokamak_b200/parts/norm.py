@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import NORMS, NormedBranch, OwedNorm, Runtime, TensorReq
+from .base import NORMS, HyperBranch, NormedBranch, OwedNorm, Runtime, TensorReq
 
 
 @dataclass(frozen=True)
@@ -203,4 +203,62 @@ class GroupRMSNorm:
             resid.add_(sum_parts(delta, torch.float32))
         ops.branch_norm_add(resid, None, None, None, 0.0, self.weight, out, self.spec.eps, rows,
                             next_groups=self.spec.groups)
+        return out
+
+
+@dataclass(frozen=True)
+class LayerNormSpec:
+    """A layer norm with a weight and, with ``bias``, a bias (the tensor's name with ``bias_suffix``)."""
+
+    dim: int
+    eps: float
+    bias: bool = True
+    bias_suffix: str = ".b"
+    kind: str = "layernorm"
+
+
+@NORMS.register("layernorm")
+class LayerNorm:
+    """``(x - mean) / sqrt(var + eps) * w + b`` with the variance the mean of the squared deviations; statistics
+    are float32 and taken in two passes over the row.
+
+    The residual stream it reads may be kept in several float32 copies ``[S, tokens, width]`` (a 2-D stream is
+    one copy): ``add_norm`` writes the pending sublayer output to all copies (a
+    :class:`~tokamak_b200.parts.base.HyperBranch`; a plain tensor joins every copy as it is), reads the row
+    ``sum_s read[s] x_s`` (``read=None``: the sum of the copies) and normalises it, in one kernel
+    (``csrc/hyper.cu``)."""
+
+    GRAPH_SAFE = True
+
+    def __init__(self, spec: LayerNormSpec, name: str, tensors: dict[str, torch.Tensor], rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+        self.weight = tensors[name]
+        self.bias = tensors[name + spec.bias_suffix] if spec.bias else None
+
+    @staticmethod
+    def expected_tensors(spec: LayerNormSpec, name: str) -> dict[str, TensorReq]:
+        out = {name: TensorReq((spec.dim,), role="vector")}
+        if spec.bias:
+            out[name + spec.bias_suffix] = TensorReq((spec.dim,), role="bias")
+        return out
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.weight, self.bias) if t is not None)
+
+    def add_norm(self, resid: torch.Tensor, delta, rows: torch.Tensor | None = None, read: torch.Tensor | None = None):
+        """Normalised rows in the engine's dtype.  Without ``rows`` the pending branch is written to the stream
+        and every row is normalised; with ``rows`` only those rows are, and the stream is left as it is."""
+        streams = resid if resid.dim() == 3 else resid.unsqueeze(0)
+        if isinstance(delta, OwedNorm):
+            delta = None        # its branch is in the stream already
+        if isinstance(delta, NormedBranch):
+            raise ValueError("a layer norm does not join a branch that is normalised on the way out")
+        if delta is not None and not isinstance(delta, HyperBranch):
+            delta = HyperBranch(delta)
+        branch = delta.x if delta is not None else None
+        out, _ = ops.hyper_mix_norm(streams, branch, mix=delta.mix if delta else None,
+                                    write=delta.write if delta else None, read=read,
+                                    mult=delta.mult if delta else 1.0, norm_w=self.weight, norm_b=self.bias,
+                                    eps=self.spec.eps, dtype=self.rt.dtype, rows=rows)
         return out

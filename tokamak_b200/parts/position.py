@@ -81,6 +81,7 @@ class RopePairsSpec:
     theta: float
     yarn: YarnScaling | None = None
     kind: str = "rope_pairs"
+    linear_factor: float = 1.0     # every frequency is divided by it (linear position scaling)
 
 
 def yarn_frequencies(rotary_dim: int, theta: float, yarn: YarnScaling | None) -> tuple[torch.Tensor, float]:
@@ -115,7 +116,7 @@ class RopePairs:
             raise ValueError(f"the rotated part of a head must be even, got {spec.rotary_dim}")
         self.spec = spec
         freq, self.magnitude = yarn_frequencies(spec.rotary_dim, spec.theta, spec.yarn)
-        self.inv_freq = freq.to(torch.float32).to(rt.device)
+        self.inv_freq = (freq / spec.linear_factor).to(torch.float32).to(rt.device)
 
     @staticmethod
     def expected_tensors(spec: RopePairsSpec) -> dict:
@@ -128,6 +129,49 @@ class RopePairs:
         table = step.scratch.get(key)
         if table is None:
             table = ops.rope_table(step.positions, self.inv_freq, self.magnitude)
+            step.scratch[key] = table
+        return table, self.spec.rotary_dim
+
+
+@dataclass(frozen=True)
+class RopeHalvesSpec:
+    """Rotation of halves (elements i and i + rotary_dim / 2) over the first ``rotary_dim`` elements of a head;
+    the rest passes unrotated.  ``linear_factor`` divides every frequency."""
+
+    rotary_dim: int
+    theta: float
+    linear_factor: float = 1.0
+    kind: str = "rope_halves"
+
+
+@POSITIONS.register("rope_halves")
+class RopeHalves:
+    """Rotary embedding in the half-split layout on part of the head: element ``i < rotary_dim / 2`` and element
+    ``i + rotary_dim / 2`` turn by ``position * theta ** (-2i / rotary_dim) / linear_factor``.  The frequencies are
+    formed in float64 and rounded to float32 once; position times frequency, cosine and sine are float32, once
+    per step.  The mixer's kernel does the rotation (``PAIRING`` tells it which elements pair up)."""
+
+    GRAPH_SAFE = True
+    PAIRING = "halves"
+
+    def __init__(self, spec: RopeHalvesSpec, tensors: dict, rt: Runtime):
+        if spec.rotary_dim % 2 or spec.rotary_dim < 0:
+            raise ValueError(f"the rotated part of a head must be even, got {spec.rotary_dim}")
+        self.spec = spec
+        freq, _ = yarn_frequencies(spec.rotary_dim, spec.theta, None)
+        self.inv_freq = (freq / spec.linear_factor).to(torch.float32).to(rt.device)
+
+    @staticmethod
+    def expected_tensors(spec: RopeHalvesSpec) -> dict:
+        return {}
+
+    def rotary_table(self, step) -> tuple[torch.Tensor | None, int]:
+        if self.spec.rotary_dim == 0:
+            return None, 0
+        key = ("rope_table", self.spec)
+        table = step.scratch.get(key)
+        if table is None:
+            table = ops.rope_table(step.positions, self.inv_freq)
             step.scratch[key] = table
         return table, self.spec.rotary_dim
 
