@@ -99,9 +99,10 @@ def attention_mixer(h, w, m, positions, ROUND=no_round):
     q = ROUND(h @ w["q"].T).view(T, H, d)
     k = ROUND(h @ w["k"].T).view(T, G, d)
     v = k.clone()
-    rot = m["rot"]
-    ang = rope_angles(positions, rot["dims"], rot["base"], (rot.get("scaling") or {}).get("factor", 1.0))
-    q, k = ROUND(rotate_neighbours(q, ang)), ROUND(rotate_neighbours(k, ang))
+    rot = m.get("rot")
+    if rot:
+        ang = rope_angles(positions, rot["dims"], rot["base"], (rot.get("scaling") or {}).get("factor", 1.0))
+        q, k = ROUND(rotate_neighbours(q, ang)), ROUND(rotate_neighbours(k, ang))
     rep = H // G
     kk, vv = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
     s = torch.einsum("ihd,jhd->hij", q, kk) * m["scale"]
@@ -240,3 +241,22 @@ def forward(cfg, weights, tokens, ROUND=no_round, layers_out=None):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return logits
+
+
+def load_folder(folder):
+    """``(config dictionary, name -> float64 tensor)`` of a model folder."""
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+    cfg = json.loads((Path(folder) / "config.json").read_text())
+    return cfg, {k: v.to(DT) for k, v in load_file(str(Path(folder) / "model.safetensors")).items()}
+
+
+def greedy_generate(cfg, weights, prompt, n_new):
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        tok = int(forward(cfg, weights, seq)[-1].argmax())
+        out.append(tok)
+        seq.append(tok)
+    return out
