@@ -1404,10 +1404,228 @@ def tarivik_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
     return rows
 
 
+# --design pukinex: the Pukinex design beside a Ketalix model of equal layer sizes (the engine's closest other
+# design: attention layers with a cap and a sink, recurrent layers on the same recurrence kernel, dense feed-forwards)
+
+def pukinex_config(s: dict) -> dict:
+    """Parallel layers (attention with a bucketed distance bias beside retention) and attention layers in turn,
+    every layer with an ungated feed-forward that holds as many weights as the twin's gated one (ff * 3 / 2); two
+    copies of the residual stream.  Attention heads as the twin's; retention has the twin's recurrent state
+    (width / 256 heads, 128 x 256)."""
+    w, d = s["width"], s["dim"]
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5 * 8.0, "softcap": 30.0,
+           "rot": {"base": 5e5, "dims": d // 2, "scaling": {"factor": 8.0}}}
+    left = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "bias_max": 2048,
+            "bias_buckets": 32, "q_temp": {"coef": 0.5, "every": 256}}
+    heads = w // 256
+    right = {"heads": heads, "dim": 128, "vdim": 256, "decay": [1.0 - 2.0 ** (-5 - (h % 6)) for h in range(heads)],
+             "rot": {"base": 1e6, "dims": 128}}
+    par = {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.5}
+    mlp = {"kind": "dense", "ff": s["ff"] * 3 // 2}
+    layers = [{"type": "parallel" if i % 2 == 0 else "attention", "mixer": par if i % 2 == 0 else att, "mlp": mlp}
+              for i in range(s["layers"])]
+    return {"architecture": "Pukinex", "vocab": s["vocab"], "width": w, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "residual_mult": 0.7, "streams": 2, "logit_scale": 0.25, "logit_softcap": 30.0, "layers": layers}
+
+
+def pukinex_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> list[dict]:
+    """Every kernel of the design alone, beside the like kernel of the Ketalix path at the same shape:
+    time, achieved bytes or flops per second, and the fraction of the measured peak."""
+    import torch
+    from types import SimpleNamespace
+    from tokamak_b200.csrc import ops
+    from tokamak_b200.parts.attention import bucketed_distance_table, paged_attention
+    from tokamak_b200.parts.base import linear
+    from tokamak_b200.cache.device import KVView
+    dev = "cuda"
+    gen = torch.Generator(device=dev).manual_seed(0)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    err = torch.zeros(4, dtype=torch.int32, device=dev)
+    hq, hkv, d, page, width = s["heads"], s["kv_heads"], s["dim"], 16, s["width"]
+    ff, ff_twin = s["ff"] * 3 // 2, s["ff"]
+    bf = lambda *shape: torch.randn(shape, device=dev, generator=gen).bfloat16()
+    f32 = lambda *shape: torch.randn(shape, device=dev, generator=gen)
+    rows = []
+
+    def row(kernel, like, us, us_like, nbytes=0, flops=0.0, like_bytes=0, like_flops=0.0, note=""):
+        r = {"kernel": kernel, "like": like, "us": round(us, 1), "like_us": round(us_like, 1) if us_like else None}
+        for name, t, fl, nb in (("", us, flops, nbytes), ("like_", us_like, like_flops or flops, like_bytes or nbytes)):
+            if not t:
+                continue
+            if fl:
+                r[name + "bf16_frac"] = round(fl / (t * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
+            elif nb:
+                r[name + "hbm_frac"] = round(nb / (t * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+        if note:
+            r["note"] = note
+        rows.append(r)
+
+    def step_of(n, n_req, start):
+        per = n // n_req
+        none = i32([])
+        rec, n_parts, n_split = ops.prefill_tc_records([r * per for r in range(n_req)], [per] * n_req, [start + per] * n_req,
+                                                       list(range(n_req)), heads=s["heads"], sms=ops.sm_count(torch.device(dev, 0)))
+        return SimpleNamespace(
+            decode_items=i32(list(range(n))) if per == 1 else none, prefill_items=none if per == 1 else i32(list(range(n))),
+            prefill_tiles=none, prefill_tc=ops.PrefillItems(torch.from_numpy(rec).to(dev), n_parts, n_split),
+            positions=i32([start + i for _ in range(n_req) for i in range(per)]),
+            tok_req=i32([r for r in range(n_req) for _ in range(per)]), req_q_start=i32([r * per for r in range(n_req)]),
+            req_q_len=i32([per] * n_req), req_kv_len=i32([start + per] * n_req), req_slot=i32(list(range(n_req))),
+            err=err, max_q_len=per, n_tokens=n, n_reqs=n_req, scratch={}, max_kv_len=start + per)
+
+    rel = f32(32, hq)
+    dist = bucketed_distance_table(rel, 2048)
+    unit, sinks = torch.zeros(hq, device=dev), f32(hq)
+    cases = (("prompt", tokens, 1, 0), ("single tokens", batch, batch, ctx - 1))
+    for name, n, n_req, start in cases:
+        single = n_req > 1
+        step = step_of(n, n_req, start)
+        pages_req = -(-(start + n // n_req) // page)
+        kc, vc = bf(n_req * pages_req, hkv, page, d), bf(n_req * pages_req, hkv, page, d)
+        table = torch.randperm(n_req * pages_req, device=dev, generator=gen).to(torch.int32).view(n_req, pages_req)
+        q = bf(n, hq, d)
+        out = torch.empty_like(q)
+        view = KVView(kc, vc, table, page, None)
+        keys = n * (start + 1) if single else n * (n + 1) // 2
+        # ---- attention with the bucketed distance bias and one in the denominator; the twin's has a cap and a sink
+        mine = lambda: paged_attention(q, out, view, step, scale=d ** -0.5, window=None, sinks=unit, dist_bias=dist)
+        like = lambda: paged_attention(q, out, view, step, scale=d ** -0.5, window=None, sinks=sinks, softcap=30.0)
+        mine(); like()
+        if single:
+            row(f"attention (bucketed distance bias, unit sink), {name}", f"attention (cap, sink), {name}",
+                _time_us(mine, graph=True), _time_us(like, graph=True), nbytes=2 * hkv * keys * d * 2 + 2 * q.numel() * 2)
+        else:
+            row(f"attention (bucketed distance bias, unit sink), {name}", f"attention (cap, sink), {name}",
+                _time_us(mine, iters=5), _time_us(like, iters=5), flops=4.0 * keys * hq * d)
+        # ---- q, k, v head by head: the left halves' form, the attention layers' form; the twin's pair rotation
+        projl = bf(n, (2 * hq + 2 * hkv) * d)
+        qb, kb, vb, qn, kn = f32(hq * d), f32(hkv * d), f32(hkv * d), f32(d), f32(d)
+        left = lambda: ops.qkv_heads(projl, q, kc, vc, step, table, q_off=0, k_off=hq * d, v_off=(hq + hkv) * d, q_bias=qb,
+                                     k_bias=kb, v_bias=vb, head_norm_eps=1e-5, q_norm=qn, k_norm=kn, temp_coef=0.5, temp_every=256)
+        inv_half = (1.0 / (5e5 ** (torch.arange(0, d // 2, 2, dtype=torch.float32) / (d // 2))) / 8.0).to(dev)
+        rot_half = ops.rope_table(step.positions, inv_half)
+        proja = bf(n, (hq + hkv) * d + hq)
+        attn = lambda: ops.qkv_heads(proja, q, kc, vc, step, table, q_off=0, k_off=hq * d, v_off=None, table=rot_half,
+                                     rotary_dim=d // 2)
+        qkv = bf(n, (hq + 2 * hkv) * d)
+        inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev)
+        rot = ops.rope_table(step.positions, inv_freq)
+        vf, lam = f32(n, hkv * d), torch.full((1,), 0.3, device=dev)
+        pairs = lambda: ops.qkv_pairs(qkv, q, kc, vc, step.positions, step.tok_req, step.req_slot, table, rot, err,
+                                      n_q_heads=hq, n_kv_heads=hkv, rotary_dim=d, unit_norm_eps=1e-6, v_first_in=vf,
+                                      v_lambda=lam, req_q_len=step.req_q_len, req_kv_len=step.req_kv_len)
+        nb = 2 * (hq + 2 * hkv) * d * n * 2
+        us_pairs = _time_us(pairs, graph=single)
+        row(f"biases + head norms + temperature + page write, {name}", f"pair rotation + unit norm + value blend + page write, {name}",
+            _time_us(left, graph=single), us_pairs, nbytes=nb, like_bytes=nb + vf.numel() * 4)
+        row(f"pair rotation on half a head + values from keys + page write, {name}",
+            f"pair rotation + unit norm + value blend + page write, {name}", _time_us(attn, graph=single), us_pairs,
+            nbytes=(2 * hq + 3 * hkv) * d * n * 2, like_bytes=nb + vf.numel() * 4)
+        # ---- gates: per channel into the stacked rows (left half), per head (attention layers)
+        att_rows = bf(n, hq * d)
+        wide = torch.empty(n, hq * d + width, dtype=torch.bfloat16, device=dev)
+        row(f"channel gate + branch factor into the stacked rows, {name}", None,
+            _time_us(lambda: ops.gate_scale(att_rows, projl, 0, out=wide[:, :hq * d], scale=0.6),
+                     graph=single), 0.0, nbytes=3 * n * hq * d * 2)
+        row(f"head gate, {name}", None,
+            _time_us(lambda: ops.gate_scale(att_rows, proja, (hq + hkv) * d, gate_group=d), graph=single), 0.0,
+            nbytes=2 * n * hq * d * 2)
+        # ---- the block's seats: write to two copies of the stream + read + layer norm; the twin's norm kernel
+        streams, branch = f32(2, n, width), bf(n, width)
+        mixm, wr, rd = f32(2, 2), f32(2), f32(2)
+        w1, b1 = torch.ones(width, device=dev), torch.zeros(width, device=dev)
+        resid = f32(n, width)
+        normed = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
+        row(f"write to 2 copies + read + layer norm, {name}", f"output norm + layer scale + residual + input norm, {name}",
+            _time_us(lambda: ops.hyper_mix_norm(streams, branch, mix=mixm * 0.1, write=wr, read=rd, mult=0.7, norm_w=w1, norm_b=b1,
+                                                eps=1e-5, dtype=torch.bfloat16), graph=single),
+            _time_us(lambda: ops.branch_norm_add(resid, branch, w1, w1, 1e-6, w1, normed, 1e-6), graph=single),
+            nbytes=n * width * (2 + 16 + 2), like_bytes=n * width * (2 + 8 + 2))
+        # ---- the ungated feed-forward beside the twin's gated one of equal weights
+        h = bf(n, width)
+        w_up, w_down = bf(ff, width) * width ** -0.5, bf(width, ff) * ff ** -0.5
+        wgu, wd = bf(2 * ff_twin, width) * width ** -0.5, bf(width, ff_twin) * ff_twin ** -0.5
+
+        def mlp():
+            y = linear(ops.unary_act(linear(h, w_up, err=err), torch.bfloat16, "relu2"), w_down, err=err)
+            ops.flush_chains()
+            return y
+
+        def gated():
+            if n <= 64:
+                splits, stages, cluster = ops.swapped_gemm_plan(2 * ff_twin, width, n)
+                a = ops.gemm_tc_swapped(wgu, h, err, splits, max_stages=stages, cluster=cluster, swiglu=True, activation="gelu_tanh")
+            elif ops.pair_gemm_takes(n, 2 * ff_twin, width, fused=True):
+                a = ops.gemm_pair(h, wgu, err, swiglu=True, activation="gelu_tanh")
+            else:
+                gu = linear(h, wgu, err=err)
+                a = torch.empty(n, ff_twin, dtype=torch.bfloat16, device=dev)
+                ops.swiglu(gu, a, block=ops.SWIGLU_TILE_BLOCK, activation="gelu_tanh")
+            y = linear(a, wd, err=err)
+            ops.flush_chains()
+            return y
+        if single:
+            row(f"feed-forward (up, relu squared, down), {name}", f"gated feed-forward of equal weights, {name}",
+                _time_us(mlp, graph=True), _time_us(gated, graph=True), nbytes=2 * ff * width * 2, like_bytes=3 * ff_twin * width * 2)
+        else:
+            row(f"feed-forward (up, relu squared, down), {name}", f"gated feed-forward of equal weights, {name}",
+                _time_us(mlp), _time_us(gated), flops=4.0 * n * ff * width, like_flops=6.0 * n * ff_twin * width)
+        up_sums = linear(h, w_up, err=err)
+        gu_twin, act_twin = bf(n, 2 * ff_twin), torch.empty(n, ff_twin, dtype=torch.bfloat16, device=dev)
+        row(f"relu squared (the kernel of its own), {name}", f"gelu gate (the kernel of its own), {name}",
+            _time_us(lambda: ops.unary_act(up_sums, torch.bfloat16, "relu2"), graph=single),
+            _time_us(lambda: ops.swiglu(gu_twin, act_twin, block=ops.SWIGLU_TILE_BLOCK, activation="gelu_tanh"), graph=single),
+            nbytes=up_sums.numel() * up_sums.element_size() + n * ff * 2, like_bytes=n * ff_twin * 3 * 2)
+        # ---- retention beside gated linear attention: inputs, recurrence (the same kernel), output stage
+        gh, gk, gv, rk = width // 256, 128, 256, 16
+        gproj = bf(n, 2 * gh * gk + 2 * gh * gv + rk) * 0.5
+        w2a, gbias = bf(gh * gk, rk) * 0.1, f32(gh * gk)
+        gprep = lambda: ops.gla_prepare(gproj, 0, gh * gk, 2 * gh * gk, 2 * gh * gk + 2 * gh * gv, w2a, gbias, heads=gh,
+                                        key_dim=gk, value_dim=gv, tau=16.0, q_scale=gk ** -0.5)
+        gstate = torch.zeros(n_req, gh, gk, gv, device=dev)
+        gp = gprep()
+        gscan = lambda: ops.gla_scan(gp, gstate, step.req_q_start, step.req_q_len, step.req_slot, err)
+        go = gscan()
+        us_gscan, us_gprep = _time_us(gscan, graph=single), _time_us(gprep, graph=single)
+        nw = torch.ones(gv, device=dev)
+        us_gout = _time_us(lambda: ops.gla_out(go, gproj, 2 * gh * gk + gh * gv, nw, 1e-6, torch.bfloat16), graph=single)
+        gla_in = n * (2 * gh * gk + gh * gv + rk) * 2 + gp.numel() * 4
+        rproj = bf(n, 2 * gh * gk + 2 * gh * gv) * 0.5
+        decay = torch.tensor([1.0 - 2.0 ** (-5 - (i % 6)) for i in range(gh)], device=dev)
+        inv_r = (1.0 / (1e6 ** (torch.arange(0, gk, 2, dtype=torch.float32) / gk))).to(dev)
+        rtab = ops.rope_table(step.positions, inv_r)
+        rprep = lambda: ops.retention_prepare(rproj, decay, rtab, dtype=torch.bfloat16, q_off=0, k_off=gh * gk, v_off=2 * gh * gk,
+                                              heads=gh, key_dim=gk, value_dim=gv, rotary_dim=gk, halves=True, k_scale=gk ** -0.5)
+        rp = rprep()
+        row(f"retention float32 inputs (rotation, scale, decay), {name}", f"gla float32 inputs, {name}",
+            _time_us(rprep, graph=single), us_gprep, nbytes=n * (2 * gh * gk + gh * gv) * 2 + rp.numel() * 4, like_bytes=gla_in)
+        rstate = torch.zeros(n_req, gh, gk, gv, device=dev)
+        rscan = lambda: ops.gla_scan(rp, rstate, step.req_q_start, step.req_q_len, step.req_slot, err)
+        ro = rscan()
+        us_rscan = _time_us(rscan, graph=single)
+        rows.append({"kernel": f"retention recurrence, {name}", "like": f"gla recurrence, {name}", "us": round(us_rscan, 1),
+                     "like_us": round(us_gscan, 1),
+                     "fp32_tflops": round(4.0 * n * gh * gk * gv / (us_rscan * 1e-6) / 1e12, 2),
+                     "like_fp32_tflops": round(4.0 * n * gh * gk * gv / (us_gscan * 1e-6) / 1e12, 2),
+                     "note": "the same kernel: float32 on the CUDA cores, token by token"})
+        row(f"retention unit norm + silu gate + branch factor into the stacked rows, {name}", f"gla output norm + gate, {name}",
+            _time_us(lambda: ops.gla_out(ro, rproj, 2 * gh * gk + gh * gv, None, 1e-5, torch.bfloat16,
+                                         out=wide[:, hq * d:hq * d + gh * gv] if gh * gv <= width else None, out_scale=0.5),
+                     graph=single), us_gout, nbytes=n * gh * gv * (4 + 2 + 2))
+        # ---- scaled and capped logits (float32, in place)
+        if single:
+            logits = f32(n, s["vocab"])
+            row(f"logit scale + cap, {name}", None, _time_us(lambda: ops.logits_scale_cap(logits, 0.25, 30.0), graph=True), 0.0,
+                nbytes=2 * logits.numel() * 4)
+    assert err.tolist()[0] == 0, err.tolist()
+    return rows
+
+
 DESIGNS = {
     "ketalix": dict(name="Ketalix", config=ketalix_config, twin=("qwen3_twin", qwen3_twin), kernels=ketalix_kernels),
     "logivik": dict(name="Logivik", config=logivik_config, twin=("ketalix_twin", ketalix_config), kernels=logivik_kernels),
     "tarivik": dict(name="Tarivik", config=tarivik_config, twin=("ketalix_twin", ketalix_config), kernels=tarivik_kernels),
+    "pukinex": dict(name="Pukinex", config=pukinex_config, twin=("ketalix_twin", ketalix_config), kernels=pukinex_kernels),
 }
 
 
@@ -1515,7 +1733,7 @@ def main() -> int:
     ap.add_argument("--sizes", default="8b", choices=["0.6b", "8b", "14b", "32b"],
                     help="layer sizes: of --workload (0.6b, 8b), or of the decode/prefill run (8b, the metric's "
                          "own, 14b, 32b)")
-    ap.add_argument("--design", default=None, choices=["ketalix", "logivik", "tarivik"],
+    ap.add_argument("--design", default=None, choices=["ketalix", "logivik", "tarivik", "pukinex"],
                     help="measure another design instead: its prefill and decode throughput beside the engine's closest "
                          "other model of equal layer sizes (Ketalix beside Qwen3, Logivik beside Ketalix), and its kernels "
                          "alone beside their like kernels (--design-sizes)")

@@ -80,11 +80,11 @@ def bucket_of(n: int, rows: int, far: int) -> int:
 def distance_bias(T, rel, far, positions):
     """[H, T, T] bias rel[bucket(i - j), h] (zero above the diagonal)."""
     rows, heads = rel.shape
-    out = torch.zeros((heads, T, T), dtype=rel.dtype)
-    for a in range(T):
-        for b in range(a + 1):
-            out[:, a, b] = rel[bucket_of(int(positions[a] - positions[b]), rows, far)]
-    return out
+    pos = torch.as_tensor(positions)
+    dist = pos[:, None] - pos[None, :]
+    buckets = torch.tensor([bucket_of(n, rows, far) for n in range(int(dist.max()) + 1)])
+    out = rel[buckets[dist.clamp_min(0)]].permute(2, 0, 1)
+    return out * (dist >= 0)
 
 
 def gelu_tanh(z):

@@ -340,6 +340,90 @@ def test_attention_with_a_bias_by_bucketed_distance_and_keys_that_stand_out(dtyp
     assert torch.allclose(lone[0, 0], 0.5 * v[0, 0].double())
 
 
+def _tiled_step(q_lens, slots, starts, heads):
+    """:func:`fake_step` with what the attention mixer's choice of kernels reads besides."""
+    from tokamak_b200.csrc import ops
+    step = fake_step(q_lens, slots, starts)
+    q_start = step.req_q_start.tolist()
+    kv_len = [s + n for s, n in zip(starts, q_lens)]
+    rec, n_parts, n_split = ops.prefill_tc_records(q_start, q_lens, kv_len, slots, heads=heads,
+                                                   sms=ops.sm_count(torch.device("cuda", 0)))
+    step.prefill_tc = ops.PrefillItems(torch.from_numpy(rec).cuda(), n_parts, n_split)
+    step.decode_items = i32([q_start[r] for r, n in enumerate(q_lens) if n == 1])
+    step.prefill_items = i32([q_start[r] + j for r, n in enumerate(q_lens) if n > 1 for j in range(n)])
+    step.prefill_tiles = i32([])
+    step.max_kv_len = max(kv_len)
+    return step
+
+
+@pytest.mark.parametrize("rows,far,cap", [(16, 100, None), (8, 300, 12.0), (32, 650, None), (4, 9, None)])
+@pytest.mark.parametrize("H,G,d", [(8, 2, 64), (4, 4, 128), (6, 1, 128)])
+def test_bucketed_distance_bias_on_the_tiled_kernels(rows, far, cap, H, G, d):
+    """bfloat16 heads of 64 and 128 channels go to the tensor-core kernels, which know the distance table too: a
+    whole prompt (key tiles wholly beyond the table's last distance, tiles that straddle it, the diagonal), a
+    portion that begins inside a page and a key tile, single tokens around every bucket's first distance (equal
+    splits and tiles dealt out), and both kinds in one step; every head has a bucket that takes the whole weight."""
+    from tokamak_b200.csrc import ops
+    from tokamak_b200.cache.device import KVView
+    from tokamak_b200.parts.attention import bucketed_distance_table, paged_attention
+    gen = torch.Generator().manual_seed(rows * 10 + H)
+    T, page = 700, 16
+    q = torch.randn(T, H, d, generator=gen).to(torch.bfloat16)
+    k = torch.randn(T, G, d, generator=gen).to(torch.bfloat16)
+    v = torch.randn(T, G, d, generator=gen).to(torch.bfloat16)
+    rel = torch.randn(rows, H, generator=gen)
+    for h in range(H):
+        rel[(rows // 2 + 3 * h) % rows, h] += 12.0
+    edges = sorted({n for n in range(1, far + 1) if plain.bucket_of(n, rows, far) != plain.bucket_of(n - 1, rows, far)})
+    probes = sorted({min(T - 1, max(0, e + j)) for e in edges[-6:] + [far] for j in (-1, 0, 1)} | {0, 1, T - 1})
+    q[T - 1] *= 2.0
+    k[3] = (q[T - 1, ::H // G].float() * 1.5).to(k.dtype)       # a key far back that stands out by its score
+    want = _biased_attention(q.double(), k.double(), v.double(), 0.2, rel.double(), far, cap)
+    n_pages = -(-T // page) + 7
+    ids = torch.randperm(n_pages, generator=gen)[:-(-T // page)]
+    kc = torch.full((n_pages, G, page, d), float("nan"), dtype=torch.bfloat16)
+    vc = torch.full((n_pages, G, page, d), float("nan"), dtype=torch.bfloat16)
+    kc[ids[-1]] = 0.0                            # the rest of a request's last page is cleared by the kernel that writes it
+    vc[ids[-1]] = 0.0
+    for p in range(T):
+        kc[ids[p // page], :, p % page] = k[p]
+        vc[ids[p // page], :, p % page] = v[p]
+    table = torch.full((3, 64), -1, dtype=torch.int32)
+    table[1, :len(ids)] = ids.int()
+    view = KVView(dev(kc), dev(vc), dev(table), page, None)
+    kw = dict(scale=0.2, window=None, softcap=cap, sinks=torch.zeros(H, device="cuda"),
+              dist_bias=bucketed_distance_table(dev(rel), far))
+
+    def run(q_lens, starts):
+        step = _tiled_step(q_lens, [1] * len(q_lens), starts, H)
+        x = torch.cat([q[s:s + n] for n, s in zip(q_lens, starts)])
+        out = torch.full((len(x), H, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+        paged_attention(dev(x), out, view, step, **kw)
+        torch.cuda.synchronize()
+        assert step.err.tolist()[0] == 0
+        close(out, torch.cat([want[s:s + n] for n, s in zip(q_lens, starts)]), "bfloat16", scale=4.0)
+        return step
+
+    assert ops.decode_kernel_takes(H, G, d, page) and ops.prefill_tc_kernel_takes(H, G, d, page)
+    run([T], [0])
+    run([T - 130], [130])
+    run([1] * len(probes), probes)
+    run([1, T - 333, 1, 1], [probes[-2], 333, probes[1], probes[len(probes) // 2]])
+    step = _tiled_step([1] * len(probes), [1] * len(probes), probes, H)
+    x = dev(torch.cat([q[i:i + 1] for i in probes]))
+    ref = torch.cat([want[i:i + 1] for i in probes])
+    args = (view.k, view.v, step.decode_items, step.positions, step.tok_req, step.req_slot, view.table, step.err)
+    for n_splits in (1, 3, 16):
+        out = torch.full_like(x, float("nan"))
+        ops.attention_decode(x, out, *args, n_splits=n_splits, **kw)
+        close(out, ref, "bfloat16", scale=4.0)
+    for blocks in (1, 5, 64):
+        out = torch.full_like(x, float("nan"))
+        ops.attention_decode_balanced(x, out, *args, blocks=blocks, **kw)
+        close(out, ref, "bfloat16", scale=4.0)
+    assert step.err.tolist()[0] == 0
+
+
 def _mixer_part(kind, spec, weights, dtype):
     from tokamak_b200.parts.base import MIXERS, Runtime
     rt = Runtime(device=torch.device("cuda"), dtype=TORCH[dtype])

@@ -54,6 +54,8 @@ struct DecodeParams {
   const float* sinks;           // [n_q_heads] or null: a term of every softmax denominator
   int chunk;                    // > 0: a token sees only the keys of its own block of that many positions
   const float* slopes;          // [n_q_heads] or null: a key n positions back loses slope * n of its score
+  const float* dist_bias;       // [n_q_heads, dist_len] or null: a key n positions back gains dist_bias[h, min(n, dist_len - 1)]
+  int dist_len;
 };
 
 template <int D, int STAGES>
@@ -82,6 +84,12 @@ attn_decode_split_kernel(DecodeParams p) {
   if (p.slopes != nullptr) {
     if (g < group) slope2[0] = p.slopes[hkv * group + g] * 1.4426950408889634f;
     if (g + 8 < group) slope2[1] = p.slopes[hkv * group + g + 8] * 1.4426950408889634f;
+  }
+  // rows of the distance table of this thread's two query heads
+  const float* dist2[2] = {nullptr, nullptr};
+  if (p.dist_bias != nullptr) {
+    if (g < group) dist2[0] = p.dist_bias + (size_t)(hkv * group + g) * p.dist_len;
+    if (g + 8 < group) dist2[1] = p.dist_bias + (size_t)(hkv * group + g + 8) * p.dist_len;
   }
 
   // key tiles of this block
@@ -199,7 +207,8 @@ attn_decode_split_kernel(DecodeParams p) {
       for (int e = 0; e < 4; ++e) {
         const int key = tile * kDecTile + nt * 8 + 2 * t4 + (e & 1);
         const bool valid = key >= lo && key <= pos;
-        s[nt][e] = valid ? capped_score_log2(s[nt][e], p.scale_log2, p.cap_log2, p.inv_cap) - slope2[e >> 1] * (float)(pos - key)
+        s[nt][e] = valid ? capped_score_log2(s[nt][e], p.scale_log2, p.cap_log2, p.inv_cap) - slope2[e >> 1] * (float)(pos - key) +
+                                   (dist2[e >> 1] != nullptr ? dist2[e >> 1][min(pos - key, p.dist_len - 1)] * 1.4426950408889634f : 0.0f)
                          : -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
       }
@@ -422,6 +431,8 @@ struct DecodeBalParams {
   const float* sinks;
   int chunk;                    // as in DecodeParams
   const float* slopes;
+  const float* dist_bias;
+  int dist_len;
 };
 
 // The block that holds tile t of the sequence of T tiles: the largest c with T c / G <= t.
@@ -519,6 +530,11 @@ attn_decode_balanced_kernel(DecodeBalParams p) {
     if (p.slopes != nullptr) {
       if (g < group) slope2[0] = p.slopes[hkv * group + g] * 1.4426950408889634f;
       if (g + 8 < group) slope2[1] = p.slopes[hkv * group + g + 8] * 1.4426950408889634f;
+    }
+    const float* dist2[2] = {nullptr, nullptr};
+    if (p.dist_bias != nullptr) {
+      if (g < group) dist2[0] = p.dist_bias + (size_t)(hkv * group + g) * p.dist_len;
+      if (g + 8 < group) dist2[1] = p.dist_bias + (size_t)(hkv * group + g + 8) * p.dist_len;
     }
     const int first_tile = lo / kDecTile;
     const int last_tile = pos / kDecTile;
@@ -619,7 +635,8 @@ attn_decode_balanced_kernel(DecodeBalParams p) {
         for (int e = 0; e < 4; ++e) {
           const int key = tile * kDecTile + nt * 8 + 2 * t4 + (e & 1);
           const bool valid = key >= lo && key <= pos;
-          s[nt][e] = valid ? capped_score_log2(s[nt][e], p.scale_log2, p.cap_log2, p.inv_cap) - slope2[e >> 1] * (float)(pos - key)
+          s[nt][e] = valid ? capped_score_log2(s[nt][e], p.scale_log2, p.cap_log2, p.inv_cap) - slope2[e >> 1] * (float)(pos - key) +
+                                   (dist2[e >> 1] != nullptr ? dist2[e >> 1][min(pos - key, p.dist_len - 1)] * 1.4426950408889634f : 0.0f)
                            : -INFINITY;
           mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
         }
@@ -861,7 +878,7 @@ TK_API int tk_attention_decode(const void* q, void* out, const void* k_cache, co
                                int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
                                int head_dim, int page_size, int max_pages, int num_pages, int window,
                                int n_splits, float scale, float softcap, const float* sinks,
-                               int chunk, const float* slopes, cudaStream_t stream) {
+                               int chunk, const float* slopes, const float* dist_bias, int dist_len, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   const int group = n_kv_heads > 0 ? n_q_heads / n_kv_heads : 0;
   if (n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || group > 16 || page_size % 16 != 0 ||
@@ -884,7 +901,7 @@ TK_API int tk_attention_decode(const void* q, void* out, const void* k_cache, co
   p.scale_log2 = scale * 1.4426950408889634f;
   p.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
   p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
-  p.sinks = sinks; p.chunk = chunk; p.slopes = slopes;
+  p.sinks = sinks; p.chunk = chunk; p.slopes = slopes; p.dist_bias = dist_bias; p.dist_len = dist_bias != nullptr ? dist_len : 0;
   if (head_dim == 128) return tk::launch_decode<128>(p, stream);
   return tk::launch_decode<64>(p, stream);
 }
@@ -902,7 +919,7 @@ TK_API int tk_attention_decode_balanced(const void* q, void* out, const void* k_
                                         int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
                                         int head_dim, int page_size, int max_pages, int num_pages, int window,
                                         int blocks, float scale, float softcap, const float* sinks,
-                                        int chunk, const float* slopes, cudaStream_t stream) {
+                                        int chunk, const float* slopes, const float* dist_bias, int dist_len, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   const int group = n_kv_heads > 0 ? n_q_heads / n_kv_heads : 0;
   if (n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || group > 16 || page_size % 16 != 0 || blocks < 1 ||
@@ -919,7 +936,7 @@ TK_API int tk_attention_decode_balanced(const void* q, void* out, const void* k_
   p.scale_log2 = scale * 1.4426950408889634f;
   p.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
   p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
-  p.sinks = sinks; p.chunk = chunk; p.slopes = slopes;
+  p.sinks = sinks; p.chunk = chunk; p.slopes = slopes; p.dist_bias = dist_bias; p.dist_len = dist_bias != nullptr ? dist_len : 0;
   if (head_dim == 128) return tk::launch_decode_balanced<128>(p, blocks, stream);
   return tk::launch_decode_balanced<64>(p, blocks, stream);
 }

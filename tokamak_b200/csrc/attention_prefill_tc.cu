@@ -84,6 +84,8 @@ struct AttnTcParams {
   const float* sinks;            // [n_q_heads] or null: a term of every softmax denominator
   int chunk;                     // > 0: a token sees only the keys of its own block of that many positions
   const float* slopes;           // [n_q_heads] or null: a key n positions back loses slope * n of its score
+  const float* dist_bias;        // [n_q_heads, dist_len] or null: a key n positions back gains dist_bias[h, min(n, dist_len - 1)]
+  int dist_len;
 };
 
 struct AttnItem {        // what a block's roles need of an item
@@ -565,6 +567,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int pos_r = my.pos0 + row;
       const int lo_r = first_visible(pos_r, p.window, p.chunk);
       const float slope_l2 = p.slopes != nullptr ? p.slopes[it.head] * 1.4426950408889634f : 0.0f;
+      const float* dist_row = p.dist_bias != nullptr ? p.dist_bias + (size_t)it.head * p.dist_len : nullptr;
       const int my_kt = my.last - my.first + 1;         // <= 0: a part without keys for this tile
       float m_ref = -INFINITY, l_sum = 0.0f;
       if (row == 0) tl_value(30, 10 + t, (unsigned)it.index);
@@ -618,9 +621,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // log2 from then on (tanh is monotonic: the maximum is the bounded raw maximum).
         // A distance bias does the same, and the maximum is then that of the biased scores.
         const bool capped = p.cap_log2 != 0.0f;
-        const bool biased = slope_l2 != 0.0f;
+        const bool biased = slope_l2 != 0.0f || dist_row != nullptr;
         const float eff_scale = (capped || biased) ? 1.0f : p.scale_log2;
-        if (biased) {
+        if (dist_row != nullptr) {
+          // a bias from a table by distance; from the table's last distance on it is one number, so a
+          // tile that lies wholly that far back needs no look-ups
+          mx = -INFINITY;
+          const int n0 = pos_r - key_first, last = p.dist_len - 1;
+          if (n0 - (kAtBN - 1) >= last) {
+            const float far_bias = dist_row[last] * 1.4426950408889634f;
+#pragma unroll
+            for (int c = 0; c < kAtBN; ++c) {
+              if (sv[c] != -INFINITY) {
+                sv[c] = capped_score_log2(sv[c], p.scale_log2, p.cap_log2, p.inv_cap) - slope_l2 * (float)(n0 - c) + far_bias;
+              }
+              mx = fmaxf(mx, sv[c]);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < kAtBN; ++c) {
+              if (sv[c] != -INFINITY) {
+                sv[c] = capped_score_log2(sv[c], p.scale_log2, p.cap_log2, p.inv_cap) - slope_l2 * (float)(n0 - c) +
+                        dist_row[min(max(n0 - c, 0), last)] * 1.4426950408889634f;
+              }
+              mx = fmaxf(mx, sv[c]);
+            }
+          }
+        } else if (biased) {
           mx = -INFINITY;
 #pragma unroll
           for (int c = 0; c < kAtBN; ++c) {
@@ -945,7 +972,8 @@ TK_API int tk_attention_prefill_tc(const void* q, void* out, const void* k_cache
                                    float* part_o, float* part_ml, int* part_count, int n_tokens, int n_records,
                                    int n_q_heads, int n_kv_heads, int head_dim, int page_size, int max_pages,
                                    int num_pages, int window, float scale, float softcap, const float* sinks,
-                                   int chunk, const float* slopes, cudaStream_t stream) {
+                                   int chunk, const float* slopes, const float* dist_bias, int dist_len,
+                                   cudaStream_t stream) {
   if (n_records <= 0) return 0;
   if (!tk_attention_prefill_tc_takes(n_q_heads, n_kv_heads, head_dim, page_size) || n_q_heads > 65535 ||
       (long long)n_records * n_q_heads > 0x3fffffffLL) {
@@ -988,7 +1016,7 @@ TK_API int tk_attention_prefill_tc(const void* q, void* out, const void* k_cache
   p.scale_log2 = scale * 1.4426950408889634f;
   p.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
   p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
-  p.sinks = sinks; p.chunk = chunk; p.slopes = slopes;
+  p.sinks = sinks; p.chunk = chunk; p.slopes = slopes; p.dist_bias = dist_bias; p.dist_len = dist_bias != nullptr ? dist_len : 0;
   const long long n_items = (long long)n_records * n_q_heads;
   const int blocks = (int)(n_items < sms[dev] ? n_items : sms[dev]);
   if (head_dim == 128) return tk::launch_prefill_tc<128>(mq, mk, mv, p, blocks, stream);

@@ -97,16 +97,16 @@ _SIGNATURES: dict[str, list] = {
     "tk_gla_out": [_P, _P, _P, c_int, c_int, c_int, _P, _P, c_int, c_float, c_int, c_int, c_int, c_float, c_int, _P],
     "tk_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_float, c_float, _P, c_int, _P, _P],
+                            c_float, c_float, _P, c_int, _P, _P, c_int, _P],
     "tk_attention_decode_balanced": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                     c_float, c_float, _P, c_int, _P, _P],
+                                     c_float, c_float, _P, c_int, _P, _P, c_int, _P],
     "tk_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_float, _P],
     "tk_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                c_float, c_float, _P, c_int, _P, _P],
+                                c_float, c_float, _P, c_int, _P, _P, c_int, _P],
     "tk_attention_prefill_tc_takes": [c_int, c_int, c_int, c_int],
     "tk_attention_prefill_tc_rows": [],
     "tk_attention_prefill_tc_keys": [],

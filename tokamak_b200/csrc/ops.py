@@ -459,6 +459,16 @@ def _want_sinks(sinks: torch.Tensor | None, n_q_heads: int) -> None:
             raise KernelError("one sink per query head is needed")
 
 
+def _want_dist_bias(dist_bias: torch.Tensor | None, n_q_heads: int) -> int:
+    """Checks a distance table ``[query heads, distances]`` and returns its number of distances (0: none)."""
+    if dist_bias is None:
+        return 0
+    _want(dist_bias, torch.float32, "dist_bias")
+    if dist_bias.dim() != 2 or dist_bias.shape[0] != n_q_heads or dist_bias.shape[1] < 1:
+        raise KernelError("the distance bias must be [query heads, distances]")
+    return dist_bias.shape[1]
+
+
 def _parts_of(x: torch.Tensor, like: torch.dtype, name: str):
     """(tensor | None, partial sums | None, number of parts, tokens, row length) of a product's
     result: a 2-D tensor in the activation type, or 3-D float32 partial sums."""
@@ -1191,7 +1201,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                      scale: float, window: int | None, n_splits: int,
                      scratch: torch.Tensor | None = None, softcap: float | None = None,
                      sinks: torch.Tensor | None = None, chunk: int | None = None,
-                     slopes: torch.Tensor | None = None) -> None:
+                     slopes: torch.Tensor | None = None,
+                     dist_bias: torch.Tensor | None = None) -> None:
     """Split-K paged attention for the single next tokens listed in ``items`` (bfloat16 only).
     ``softcap``, ``sinks``, ``chunk`` and ``slopes`` as in :func:`attention_plain`."""
     _want_sinks(sinks, q.shape[1])
@@ -1221,7 +1232,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                                          req_slot.numel(), hq, hkv, d, page_size, block_table.shape[1],
                                          num_pages, int(window or 0), n_splits, float(scale),
                                          float(softcap or 0.0), _ptr(sinks), int(chunk or 0), _ptr(slopes),
-                                         _stream()),
+                                         _ptr(dist_bias), _want_dist_bias(dist_bias, hq), _stream()),
            "attention_decode")
 
 
@@ -1272,7 +1283,8 @@ def attention_decode_balanced(q: torch.Tensor, out: torch.Tensor, k_cache: torch
                               req_slot: torch.Tensor, block_table: torch.Tensor, err: torch.Tensor, *,
                               scale: float, window: int | None, blocks: int, softcap: float | None = None,
                               sinks: torch.Tensor | None = None, chunk: int | None = None,
-                              slopes: torch.Tensor | None = None) -> None:
+                              slopes: torch.Tensor | None = None,
+                     dist_bias: torch.Tensor | None = None) -> None:
     """Paged attention for the single next tokens listed in ``items`` (bfloat16 only), the key tiles of
     all (token, kv head) pairs dealt out evenly over ``blocks`` blocks.  ``softcap``, ``sinks``, ``chunk``
     and ``slopes`` as in :func:`attention_plain`."""
@@ -1302,7 +1314,8 @@ def attention_decode_balanced(q: torch.Tensor, out: torch.Tensor, k_cache: torch
                                             block_table.data_ptr(), err.data_ptr(), n_items, req_slot.numel(),
                                             hq, hkv, d, page_size, block_table.shape[1], num_pages,
                                             int(window or 0), blocks, float(scale), float(softcap or 0.0),
-                                            _ptr(sinks), int(chunk or 0), _ptr(slopes), _stream()),
+                                            _ptr(sinks), int(chunk or 0), _ptr(slopes), _ptr(dist_bias),
+                                            _want_dist_bias(dist_bias, hq), _stream()),
            "attention_decode_balanced")
 
 
@@ -1426,7 +1439,8 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tens
                          items: PrefillItems, block_table: torch.Tensor, err: torch.Tensor, *,
                          scale: float, window: int | None, softcap: float | None = None,
                          sinks: torch.Tensor | None = None, chunk: int | None = None,
-                         slopes: torch.Tensor | None = None) -> None:
+                         slopes: torch.Tensor | None = None,
+                     dist_bias: torch.Tensor | None = None) -> None:
     """Paged flash attention on tcgen05 for the work list ``items`` (see :func:`prefill_tc_records`),
     a persistent kernel that deals the items out to one block per SM.  Loads whole pages: the cache
     must have been written by :func:`rope_kv` with ``req_q_len`` and ``req_kv_len`` given.  One call
@@ -1450,7 +1464,7 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tens
                                           n, items.records.shape[0], hq, hkv, d, page_size,
                                           block_table.shape[1], num_pages, int(window or 0),
                                           float(scale), float(softcap or 0.0), _ptr(sinks), int(chunk or 0),
-                                          _ptr(slopes), _stream()),
+                                          _ptr(slopes), _ptr(dist_bias), _want_dist_bias(dist_bias, hq), _stream()),
            "attention_prefill_tc")
 
 

@@ -596,7 +596,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     the value heads have a size of their own.  ``chunk`` (a query sees only its own block of that many
     positions) and ``slopes`` (a distance bias per query head) are known to the general kernel, the decode
     kernels and the tcgen05 prefill kernel.  ``dist_bias`` (float32 ``[Hq, L]``: the score of the key ``n``
-    positions back gains ``dist_bias[h, min(n, L - 1)]``) is known to the general kernel.
+    positions back gains ``dist_bias[h, min(n, L - 1)]``) is known to the same kernels.
 
     Chooses the kernels.  A latent cache in bfloat16 goes to the tensor-core kernel that stacks the heads
     of a token (``csrc/attention_latent.cu``).  bfloat16 with a head_dim the tiled kernels take: single next
@@ -626,10 +626,11 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     # the tiled kernels take heads of one size for keys and values; of the two prefill kernels the
     # tcgen05 one knows caps and sinks
     same_size = cache_view.v.shape[3] == d
-    extras = softcap is not None or sinks is not None or chunk is not None or slopes is not None
+    extras = (softcap is not None or sinks is not None or chunk is not None or slopes is not None
+              or dist_bias is not None)
     # a single token sees no more keys than its chunk holds: the kernels' work is planned for that many
     dec_span = step.max_kv_len if chunk is None else min(step.max_kv_len, chunk)
-    tiled = bf16 and same_size and dist_bias is None
+    tiled = bf16 and same_size
     dec_tiled = tiled and n_dec > 0 and ops.decode_kernel_takes(hq, hkv, d, page)
     pf_tiled = (tiled and n_pf > 0 and ops.prefill_kernel_takes(hq, hkv, d, page)
                 and (not extras or ops.prefill_tc_kernel_takes(hq, hkv, d, page)))
@@ -647,18 +648,18 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
                 ops.attention_decode_balanced(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
                                               step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
                                               window=window, softcap=softcap, sinks=sinks, chunk=chunk, slopes=slopes,
-                                              blocks=ops.decode_balanced_blocks(q.device, n_dec, hkv, dec_span))
+                                              dist_bias=dist_bias, blocks=ops.decode_balanced_blocks(q.device, n_dec, hkv, dec_span))
             else:
                 ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
                                      step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
                                      window=window, softcap=softcap, sinks=sinks, chunk=chunk, slopes=slopes,
-                                     n_splits=ops.decode_splits(n_dec, hkv, dec_span))
+                                     dist_bias=dist_bias, n_splits=ops.decode_splits(n_dec, hkv, dec_span))
             if beside:
                 join.record()
     if pf_tiled and ops.prefill_tc_kernel_takes(hq, hkv, d, page):
         ops.attention_prefill_tc(q, out, cache_view.k, cache_view.v, step.prefill_tc,
                                  cache_view.table, step.err, scale=scale, window=window, softcap=softcap,
-                                 sinks=sinks, chunk=chunk, slopes=slopes)
+                                 sinks=sinks, chunk=chunk, slopes=slopes, dist_bias=dist_bias)
     elif pf_tiled:
         ops.attention_prefill(q, out, cache_view.k, cache_view.v, step.prefill_tiles,
                               step.req_q_start, step.req_q_len, step.req_kv_len, step.req_slot,
