@@ -203,6 +203,9 @@ def _read_pages(cache, table_row, T, page):
     (3, 1, 70, 33, 70, True, True, False, True, (2.0, 1), False),    # halves over the whole head, unit norm
     (2, 2, 16, 16, 6, True, False, False, True, None, True),
     (5, 5, 7, 9, 0, False, True, True, False, None, False),          # an odd head size
+    (4, 2, 64, 32, 0, False, True, True, True, (0.5, 3), False),     # sizes in steps of 4: 16-byte accesses
+    (2, 1, 128, 128, 64, False, False, False, False, None, True),
+    (3, 3, 20, 8, 12, True, True, True, True, None, False),
 ])
 def test_queries_keys_and_values_head_by_head(dtype, H, G, d, dv, rot, halves, norm, weight, bias, temp, from_keys):
     """Biases, head norms, temperature, both rotations over part of a head, values that are the unrotated
@@ -211,7 +214,7 @@ def test_queries_keys_and_values_head_by_head(dtype, H, G, d, dv, rot, halves, n
     gen = torch.Generator().manual_seed(H * 100 + d)
     page, T, eps = 4, 13, 1e-5
     nq, nk, nv = H * d, G * d, 0 if from_keys else G * dv
-    seqs = [torch.randn(T, nq + nk + nv + 5, generator=gen).to(TORCH[dtype]) for _ in range(2)]
+    seqs = [torch.randn(T, nq + nk + nv + (4 if d % 4 == 0 else 5), generator=gen).to(TORCH[dtype]) for _ in range(2)]
     qb = torch.randn(nq, generator=gen) if bias else None
     kb = torch.randn(nk, generator=gen) if bias else None
     vb = torch.randn(nv, generator=gen) if bias and not from_keys else None
@@ -494,6 +497,33 @@ def test_retention_decay_of_a_write_far_back_float32():
     for h, a in enumerate((0.99, 1.0)):
         want = vals.double() * 0.5 * dk * 0.25 * a ** 300
         assert (o[-1, h] - want).abs().max() <= 1e-4 * want.abs().max()
+
+
+@pytest.mark.parametrize("activation", ["relu2", "gelu_tanh", "silu"])
+@pytest.mark.parametrize("width,ff,n", [(128, 256, 9), (64, 384, 64), (256, 3072, 2048), (128, 200, 700)])
+def test_ungated_activation_in_the_products_epilogues(activation, width, ff, n):
+    """bfloat16: few tokens take the tcgen05 product whose cluster applies the activation to its summed splits,
+    many tokens the product on pairs of SMs that applies it to its accumulators; other sizes the kernel of its
+    own.  All against the plain product and activation."""
+    from tokamak_b200.csrc import ops
+    from tokamak_b200.parts.base import FEED_FORWARDS, Runtime
+    from tokamak_b200.parts.feedforward import MlpSpec
+    gen = torch.Generator().manual_seed(width + n)
+    w = _random_weights({"up": ((ff, width), width ** -0.5, 0), "down": ((width, ff), ff ** -0.5, 0)}, gen, "bfloat16")
+    rt = Runtime(device=torch.device("cuda"), dtype=torch.bfloat16)
+    part = FEED_FORWARDS.get("mlp")(MlpSpec(width, ff, activation=activation), "f.",
+                                    {"f." + k: dev(v, torch.bfloat16) for k, v in w.items()}, rt)
+    x = torch.randn(n, width, generator=gen).to(torch.bfloat16)
+    step = SimpleNamespace(err=torch.zeros(4, dtype=torch.int32, device="cuda"), scratch={}, n_tokens=n)
+    before = ops.LAUNCHES
+    got = torch.as_tensor(part.forward(dev(x), step)).float().reshape(-1, n, width).sum(0)
+    fused = ff % 128 == 0 and (n <= 64 or ops.pair_gemm_takes(n, ff, width, fused=True))
+    assert step.err.tolist()[0] == 0
+    z = x.double() @ w["up"].double().T
+    act = {"relu2": torch.relu(z) ** 2, "gelu_tanh": plain.gelu_tanh(z), "silu": z * torch.sigmoid(z)}[activation]
+    close(got, plain.bf16_round(act) @ w["down"].double().T, "bfloat16", scale=2.0)
+    if fused and n <= 64:
+        assert ops.LAUNCHES - before == 2        # two products, no kernel between them
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

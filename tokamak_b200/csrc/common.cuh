@@ -115,6 +115,12 @@ __device__ __forceinline__ float glu_act(float g, int act) {
   return g / (1.0f + expf(-g));
 }
 
+// Activations of an ungated unit: 0 = silu, 1 = the tanh form of gelu, 2 = relu(z)^2.
+__device__ __forceinline__ float unary_act(float z, int act) {
+  if (act == 2) { const float r = fmaxf(z, 0.0f); return r * r; }
+  return glu_act(z, act);
+}
+
 // Two float32 operations in one instruction (sm_100): kernels that are bound by the
 // instructions they issue (the softmax warps of the tiled attention, the recurrence of gated linear
 // attention) halve their multiply-adds and additions with these.

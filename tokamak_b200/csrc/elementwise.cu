@@ -234,11 +234,6 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, const float* __restr
 
 // Ungated feed-forward activations, out[t, j] = act(x[t, j]): 0 = silu, 1 = the tanh form of gelu, 2 = relu(x)^2.
 // x may be the float32 partial sums of a split-K product.
-__device__ __forceinline__ float unary_act(float z, int act) {
-  if (act == 2) { const float r = fmaxf(z, 0.0f); return r * r; }
-  return glu_act(z, act);
-}
-
 template <typename T>
 __global__ void unary_act_kernel(const T* __restrict__ x, const float* __restrict__ parts, int n_parts,
                                  size_t part_stride, T* __restrict__ out, size_t total, int act) {

@@ -48,6 +48,7 @@ struct GemmPairParams {
   int rows, cols, k;
   long long ld_out;
   int mode;                 // 0: bf16 [rows, cols]; 1, 2: gated activation (silu, gelu: glu_act(mode - 1)), bf16 [rows, cols / 2]
+  int unary;                // mode 0: 0 = the sums as they are, else unary_act(sum, unary - 1)
   const int* tile_expert;   // [ceil(rows / 256)] or null: the expert of every 256-row tile of x, negative: skipped
 };
 
@@ -261,12 +262,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
               __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                h2[e] = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 2 * e]), __uint_as_float(v[q * 8 + 2 * e + 1]));
+                float a0 = __uint_as_float(v[q * 8 + 2 * e]), a1 = __uint_as_float(v[q * 8 + 2 * e + 1]);
+                if (p.unary != 0) { a0 = unary_act(a0, p.unary - 1); a1 = unary_act(a1, p.unary - 1); }
+                h2[e] = __floats2bfloat162_rn(a0, a1);
               }
               *reinterpret_cast<uint4*>(orow + col) = o;
             } else {
               for (int e = 0; e < 8; ++e) {
-                if (col + e < p.cols) orow[col + e] = __float2bfloat16_rn(__uint_as_float(v[q * 8 + e]));
+                float a = __uint_as_float(v[q * 8 + e]);
+                if (p.unary != 0) a = unary_act(a, p.unary - 1);
+                if (col + e < p.cols) orow[col + e] = __float2bfloat16_rn(a);
               }
             }
           }
@@ -311,6 +316,9 @@ static int gemm_bf16_pair_launch(const void* x, const void* w, void* out, int* e
                                  long long ld_x, long long ld_w, long long ld_out, int mode, const int* tile_expert,
                                  int experts, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
+  // modes 3, 4, 5: the plain product with an ungated activation (silu, gelu, relu squared) on its sums
+  const int unary = mode >= 3 && mode <= 5 ? mode - 2 : 0;
+  if (unary != 0) mode = 0;
   if (k <= 0 || k % 8 != 0 || ld_out % 8 != 0 || mode < 0 || mode > 2 || (mode != 0 && cols % 128 != 0) ||
       ((uintptr_t)out & 15u) != 0) {
     return (int)cudaErrorInvalidValue;
@@ -343,7 +351,7 @@ static int gemm_bf16_pair_launch(const void* x, const void* w, void* out, int* e
   const int n_tiles = ((rows + 255) / 256) * ((cols + 255) / 256);
   const int pairs = n_tiles < max_pairs ? n_tiles : max_pairs;
   tk::GemmPairParams p;
-  p.out = out; p.err = err; p.rows = rows; p.cols = cols; p.k = k; p.ld_out = ld_out; p.mode = mode;
+  p.out = out; p.err = err; p.rows = rows; p.cols = cols; p.k = k; p.ld_out = ld_out; p.mode = mode; p.unary = unary;
   p.tile_expert = tile_expert;
   // the two blocks of a pair are neighbours along x, as tcgen05's cta_group::2 wants them
   return (int)tk::launch_cluster(tk::gemm_pair_kernel, dim3(2 * pairs, 1, 1), dim3(tk::kGpThreads), smem_bytes, stream,

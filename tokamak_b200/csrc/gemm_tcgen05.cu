@@ -79,6 +79,8 @@ struct GemmTcParams {
   int cluster_reduce;       // 0, or the cluster size: that many consecutive splits of a tile
                             // form a cluster and store their sum as one part (n_splits / cluster parts)
   int glu_act;              // epilogue 1: the activation of the gate, see glu_act (0 = silu, 1 = gelu, tanh form)
+  int unary;                // epilogue 1: 0 = gated; else the tile's 128 rows are outputs of their own, out is
+                            // bf16 [cols, rows] = unary_act(sum, unary - 1)
   int epilogue;             // 0 = float32 sums; 1 = gated activation, see kGtEpiSwiglu;
                             // 2 = residual sum and preparation of the next norm, see kGtEpiResidualNorm
   // every column (token) of the sums is multiplied by
@@ -364,8 +366,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
       // as without the activation, and the activation is the formula of the separate kernel
       const int t = (warp - 2) * 32 + lane;
       const int j4 = (t & 15) * 4, phase = t >> 4;
-      const int inter = p.rows_total >> 1;
-      const int oc = tile_r * 64 + j4;
+      const bool unary = p.unary != 0;
+      const int inter = unary ? p.rows_total : p.rows_total >> 1;
+      const int oc = unary ? tile_r * kGtBM + j4 : tile_r * 64 + j4;
       __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
       if (oc < inter) {                    // inter is a multiple of 64: all four outputs exist
         for (int c = (int)my_rank + csize * phase; c < p.bn; c += 8 * csize) {
@@ -379,6 +382,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
             u.x *= sc; u.y *= sc; u.z *= sc; u.w *= sc;
           }
           uint2 packed;
+          if (unary) {
+            // the rows of the tile's second half are outputs too: both halves get the activation
+            const int a = p.unary - 1;
+            *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(unary_act(u.x, a), unary_act(u.y, a));
+            *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(unary_act(u.z, a), unary_act(u.w, a));
+            *reinterpret_cast<uint2*>(out + (size_t)col * inter + oc + 64) = packed;
+            *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(unary_act(g.x, a), unary_act(g.y, a));
+            *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(unary_act(g.z, a), unary_act(g.w, a));
+            *reinterpret_cast<uint2*>(out + (size_t)col * inter + oc) = packed;
+            continue;
+          }
           *reinterpret_cast<__nv_bfloat162*>(&packed.x) =
               __floats2bfloat162_rn(glu_act(g.x, p.glu_act) * u.x, glu_act(g.y, p.glu_act) * u.y);
           *reinterpret_cast<__nv_bfloat162*>(&packed.y) =
@@ -585,7 +599,8 @@ static int launch_gemm(const void* r, const void* c, int rows, int cols, int k, 
 // of n_splits): that many consecutive splits form a thread-block cluster and store their sum.
 // epilogue = 1 (rows a multiple of 128 whose gate and up rows alternate in blocks of 64, all
 // splits in one cluster): out is bfloat16 [cols, rows / 2] = silu(gate) * up; epilogue = 4: the same with
-// the tanh form of gelu in silu's place.
+// the tanh form of gelu in silu's place.  epilogue = 5, 6, 7 (rows a multiple of 128, all splits in one cluster): out is
+// bfloat16 [cols, rows] = act(sum) with act = silu, the tanh form of gelu, relu squared.
 // epilogue = 2 (rows a multiple of 128, all splits in one cluster): nothing goes to out; the
 // sums are added to resid [cols, rows] (float32) in place, xb_out [cols, rows] receives
 // bf16(resid * norm_w) and sumsq_out [rows / 128, cols] the tiles' sums of squares of resid.
@@ -601,13 +616,17 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
                                 float* sumsq_out, cudaStream_t stream) {
   const bool gelu = epilogue == tk::kGtEpiGeglu;
   if (gelu) epilogue = tk::kGtEpiSwiglu;
+  // epilogues 5, 6, 7: an ungated activation (silu, gelu, relu squared) on the sums of every row, stored as
+  // bfloat16 [cols, rows]; they run as the gated epilogue with both halves of a tile as outputs
+  const int unary = epilogue >= 5 && epilogue <= 7 ? epilogue - 4 : 0;
+  if (unary != 0) epilogue = tk::kGtEpiSwiglu;
   if (epilogue < 0 || epilogue > tk::kGtEpiResidualNorm) return (int)cudaErrorInvalidValue;
   if (epilogue == tk::kGtEpiResidualNorm &&
       (resid == nullptr || norm_w == nullptr || xb_out == nullptr || sumsq_out == nullptr)) {
     return (int)cudaErrorInvalidValue;
   }
   tk::GemmTcParams p = {};
-  p.out = out; p.err = err; p.epilogue = epilogue; p.glu_act = gelu ? 1 : 0;
+  p.out = out; p.err = err; p.epilogue = epilogue; p.glu_act = gelu ? 1 : 0; p.unary = unary;
   p.colscale_parts = colscale_parts; p.n_colscale_parts = n_colscale_parts; p.colscale_inv_dim = colscale_inv_dim;
   p.colscale_eps = colscale_eps; p.resid = resid; p.norm_w = norm_w; p.xb_out = (__nv_bfloat16*)xb_out; p.sumsq_out = sumsq_out;
   return tk::launch_gemm(r, c, rows, cols, k, ld_r, ld_c, bn, n_splits, max_stages, cluster_reduce, p, stream);

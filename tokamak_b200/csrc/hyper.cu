@@ -98,6 +98,110 @@ __global__ void hyper_mix_norm_kernel(HyperParams p) {
   }
 }
 
+constexpr int kHyperChunks = 4;     // pieces of four columns a thread keeps in registers
+
+// The same for rows whose width is a multiple of 4 and at most 16 columns a thread: 16-byte accesses, the read
+// row stays in registers between the passes (sum, squared deviations, store), the norm's weight and bias are
+// asked for before the wait for the kernel in front.  The sums per column are formed in the same order as in
+// the kernel above, so both give the same stream.
+template <typename T>
+__global__ void __launch_bounds__(512) hyper_mix_norm_vec_kernel(HyperParams p) {
+  __shared__ float scratch[32];
+  __shared__ float s_mix[kHyperMaxStreams * kHyperMaxStreams], s_write[kHyperMaxStreams], s_read[kHyperMaxStreams];
+  pdl_trigger();
+  const int S = p.n_streams;
+  const int chunks = p.width >> 2;
+  float4 w4[kHyperChunks], b4[kHyperChunks];
+#pragma unroll
+  for (int k = 0; k < kHyperChunks; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    w4[k] = b4[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (i < chunks && p.norm_w != nullptr) {
+      w4[k] = reinterpret_cast<const float4*>(p.norm_w)[i];
+      if (p.norm_b != nullptr) b4[k] = reinterpret_cast<const float4*>(p.norm_b)[i];
+    }
+  }
+  if (threadIdx.x < S * S) {
+    const int a = threadIdx.x / S, b = threadIdx.x - a * S;
+    s_mix[threadIdx.x] = p.mix != nullptr ? p.mix[threadIdx.x] : (a == b ? 1.0f : 0.0f);
+  }
+  if (threadIdx.x < S) {
+    s_write[threadIdx.x] = (p.write != nullptr ? p.write[threadIdx.x] : 1.0f) * p.mult;
+    s_read[threadIdx.x] = p.read != nullptr ? p.read[threadIdx.x] : 1.0f;
+  }
+  pdl_wait();
+  __syncthreads();
+  const int t = p.rows != nullptr ? p.rows[blockIdx.x] : blockIdx.x;
+  if (t < 0 || t >= p.n_tokens) return;
+  const bool pending = p.branch.x != nullptr || p.branch.parts != nullptr;
+  const bool store = pending && p.rows == nullptr;
+  const size_t copy = (size_t)p.n_tokens * p.width;
+  float* x = p.streams + (size_t)t * p.width;
+  float4 u[kHyperChunks];
+  float sum = 0.0f;
+#pragma unroll
+  for (int k = 0; k < kHyperChunks; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    u[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (i >= chunks) continue;
+    float4 old[kHyperMaxStreams];
+#pragma unroll
+    for (int s = 0; s < kHyperMaxStreams; ++s) {
+      if (s < S) old[s] = *reinterpret_cast<const float4*>(x + (size_t)s * copy + 4 * i);
+    }
+    if (pending) {
+      const float4 y = stacked_ld4<T>(p.branch, (size_t)t * p.branch.row_stride + 4 * i);
+#pragma unroll
+      for (int to = 0; to < kHyperMaxStreams; ++to) {
+        if (to < S) {
+          float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+          for (int s = 0; s < kHyperMaxStreams; ++s) {
+            if (s < S) {
+              const float m = s_mix[s * S + to];
+              v.x += m * old[s].x; v.y += m * old[s].y; v.z += m * old[s].z; v.w += m * old[s].w;
+            }
+          }
+          const float wr = s_write[to], rd = s_read[to];
+          v.x += wr * y.x; v.y += wr * y.y; v.z += wr * y.z; v.w += wr * y.w;
+          if (store) *reinterpret_cast<float4*>(x + (size_t)to * copy + 4 * i) = v;
+          u[k].x += rd * v.x; u[k].y += rd * v.y; u[k].z += rd * v.z; u[k].w += rd * v.w;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int s = 0; s < kHyperMaxStreams; ++s) {
+        if (s < S) {
+          const float rd = s_read[s];
+          u[k].x += rd * old[s].x; u[k].y += rd * old[s].y; u[k].z += rd * old[s].z; u[k].w += rd * old[s].w;
+        }
+      }
+    }
+    sum += (u[k].x + u[k].y) + (u[k].z + u[k].w);
+    if (p.sum_out != nullptr) *reinterpret_cast<float4*>(p.sum_out + (size_t)blockIdx.x * p.width + 4 * i) = u[k];
+  }
+  if (p.norm_w == nullptr) return;
+  const float mean = block_sum(sum, scratch) / (float)p.width;
+  float dev = 0.0f;
+#pragma unroll
+  for (int k = 0; k < kHyperChunks; ++k) {
+    if ((int)(threadIdx.x + k * blockDim.x) < chunks) {
+      u[k].x -= mean; u[k].y -= mean; u[k].z -= mean; u[k].w -= mean;
+      dev += (u[k].x * u[k].x + u[k].y * u[k].y) + (u[k].z * u[k].z + u[k].w * u[k].w);
+    }
+  }
+  const float rstd = rsqrtf(block_sum(dev, scratch) / (float)p.width + p.eps);
+  T* out = (T*)p.out + (size_t)blockIdx.x * p.width;
+#pragma unroll
+  for (int k = 0; k < kHyperChunks; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < chunks) {
+      st4<T>(out + 4 * i, make_float4(u[k].x * rstd * w4[k].x + b4[k].x, u[k].y * rstd * w4[k].y + b4[k].y,
+                                            u[k].z * rstd * w4[k].z + b4[k].z, u[k].w * rstd * w4[k].w + b4[k].w));
+    }
+  }
+}
+
 // logits <- cap * tanh(scale * logits / cap)  (cap <= 0: only the scale), float32 in place
 __global__ void logits_scale_cap_kernel(float* __restrict__ logits, long long n, float scale, float cap) {
   pdl_trigger();
@@ -128,11 +232,23 @@ TK_API int tk_hyper_mix_norm(float* streams, const void* y, const float* y_parts
   p.mix = mix; p.write = write; p.read = read; p.norm_w = norm_w; p.norm_b = norm_b; p.out = out; p.sum_out = sum_out;
   p.rows = rows; p.n_rows = n_rows; p.n_tokens = n_tokens; p.width = width; p.n_streams = n_streams;
   p.mult = mult; p.eps = eps;
+  cudaError_t e = cudaSuccess;
+  // rows of a multiple of four columns (and a branch whose rows start at such multiples): 16-byte accesses, the
+  // row in registers; few rows get a thread per piece of four columns, many rows two pieces a thread
+  const int chunks = width / 4;
+  const bool aligned = width % 4 == 0 && ((y == nullptr && y_parts == nullptr) || y_row_stride % 4 == 0);
+  if (aligned && chunks <= 512 * tk::kHyperChunks) {
+    int threads = ((n_rows <= 296 ? chunks : (chunks + 1) / 2) + 31) / 32 * 32;
+    if (threads > 512) threads = 512;
+    if (threads < 64) threads = 64;
+    if (dtype == tk::kF32) e = tk::launch(tk::hyper_mix_norm_vec_kernel<float>, dim3((unsigned)n_rows), dim3(threads), 0, stream, p);
+    else if (dtype == tk::kBF16) e = tk::launch(tk::hyper_mix_norm_vec_kernel<__nv_bfloat16>, dim3((unsigned)n_rows), dim3(threads), 0, stream, p);
+    else return (int)cudaErrorInvalidValue;
+    return (int)e;
+  }
   const size_t smem = (size_t)width * sizeof(float);
-  // a step of few tokens fills few SMs: more threads a row then
   int threads = n_rows <= 64 ? 512 : 256;
   while (threads > 64 && threads / 2 >= width) threads /= 2;
-  cudaError_t e = cudaSuccess;
 #define TK_HYPER(T)                                                                                                    \
   do {                                                                                                                 \
     if (smem > 48 * 1024) {                                                                                            \

@@ -1713,7 +1713,8 @@ MOE_SMALL_PAIRS = 8
 def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int,
                     out: torch.Tensor | None = None, max_stages: int = 0, cluster: int = 0,
                     swiglu: bool = False, activation: str = "silu", colscale: tuple | None = None,
-                    residual_norm: tuple | None = None, chain: "ProductChain | None" = None):
+                    residual_norm: tuple | None = None, chain: "ProductChain | None" = None,
+                    unary: str | None = None):
     """``x @ weight^T`` on tcgen05, the weight being the 128-row operand (for few tokens: every
     weight byte is streamed once by TMA), as float32 partial sums ``[parts, tokens, N_out]`` for
     the caller to add up.  ``parts = n_splits``, or ``n_splits / cluster`` with ``cluster`` in
@@ -1723,6 +1724,9 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
     ``swiglu=True``: the weight is a stacked gate/up matrix whose rows alternate in blocks of
     ``SWIGLU_TILE_BLOCK`` (gate rows, then the up rows of the same outputs); all splits form one
     cluster and the result is bfloat16 ``[tokens, N_out / 2] = silu(gate) * up``.
+
+    ``unary`` (a name of ``UNARY_ACTIVATIONS``; ``N_out`` a multiple of 128, all splits in one cluster): the result
+    is bfloat16 ``[tokens, N_out] = act(sums)``.
 
     ``colscale=(sumsq, dim, eps)`` with ``sumsq`` float32 ``[tiles, tokens]``: every token's sums
     are multiplied by ``rsqrt(sum over tiles / dim + eps)`` (all splits in one cluster): ``x``
@@ -1773,6 +1777,12 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
         if activation not in GLU_ACTIVATIONS:
             raise KernelError(f"unknown activation {activation!r}")
         epilogue, out_ptr, result = (1 if activation == "silu" else 4), out.data_ptr(), out
+    elif unary is not None:
+        if n_out % 128 or parts != 1 or unary not in UNARY_ACTIVATIONS:
+            raise KernelError("the fused ungated activation wants rows in steps of 128, one cluster and a known name")
+        if out is None:
+            out = torch.empty((tokens, n_out), dtype=torch.bfloat16, device=x.device)
+        epilogue, out_ptr, result, chain = 5 + UNARY_ACTIVATIONS[unary], out.data_ptr(), out, None
     else:
         if out is None:
             out = torch.empty((parts, tokens, n_out), dtype=torch.float32, device=x.device)
@@ -2025,10 +2035,11 @@ def pair_gemm_takes(tokens: int, n_out: int, k: int, fused: bool = False) -> boo
 
 
 def gemm_pair(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, swiglu: bool = False,
-              activation: str = "silu") -> torch.Tensor:
+              activation: str = "silu", unary: str | None = None) -> torch.Tensor:
     """``x @ weight^T`` for many tokens on pairs of SMs (tcgen05.mma.cta_group::2, persistent grid);
     bfloat16 ``[tokens, N_out]``.  ``swiglu=True``: the weight is a stacked gate/up matrix whose rows
-    alternate in blocks of ``SWIGLU_TILE_BLOCK``; the result is ``[tokens, N_out / 2] = silu(gate) * up``."""
+    alternate in blocks of ``SWIGLU_TILE_BLOCK``; the result is ``[tokens, N_out / 2] = silu(gate) * up``.
+    ``unary`` (a name of ``UNARY_ACTIVATIONS``): the result is ``act(x @ weight^T)``."""
     _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
     n_out, k = weight.shape
     tokens, kx = x.shape
@@ -2040,6 +2051,10 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, swiglu: 
     if swiglu and activation not in GLU_ACTIVATIONS:
         raise KernelError(f"unknown activation {activation!r}")
     mode = 1 + GLU_ACTIVATIONS[activation] if swiglu else 0
+    if unary is not None:
+        if swiglu or unary not in UNARY_ACTIVATIONS:
+            raise KernelError(f"an ungated activation {unary!r} beside a gated one, or unknown")
+        mode = 3 + UNARY_ACTIVATIONS[unary]
     if width % 8:
         raise KernelError("the output width must be a multiple of 8")
     out = torch.empty((tokens, width), dtype=torch.bfloat16, device=x.device)

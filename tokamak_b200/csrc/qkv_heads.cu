@@ -125,6 +125,113 @@ __global__ void qkv_heads_kernel(QkvHeadsParams p) {
   }
 }
 
+// The same with 16-byte accesses, for head sizes, column offsets and row lengths that are multiples of 4: a lane
+// keeps up to four pieces of four elements of its head in registers; rotation partners are read from the
+// warp's copy of the head in shared memory.  Sums and products are formed as in the kernel above.
+template <typename T>
+__global__ void qkv_heads_vec_kernel(QkvHeadsParams p) {
+  __shared__ __align__(16) float s_head[kHeadsWarps][kHeadsMaxDim];
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int own_v = p.v_off >= 0 ? p.n_kv_heads : 0;
+  const int heads_total = p.n_q_heads + p.n_kv_heads + own_v;
+  const int t = blockIdx.x;
+  const int h = blockIdx.y * kHeadsWarps + warp;
+  if (h >= heads_total) return;
+  int kind, head;     // 0 = q, 1 = k, 2 = v
+  if (h < p.n_q_heads) { kind = 0; head = h; }
+  else if (h < p.n_q_heads + p.n_kv_heads) { kind = 1; head = h - p.n_q_heads; }
+  else { kind = 2; head = h - p.n_q_heads - p.n_kv_heads; }
+  const int d = kind == 2 ? p.v_dim : p.k_dim;
+  const int col = (kind == 0 ? p.q_off : kind == 1 ? p.k_off : p.v_off) + head * d;
+  const float* bias = kind == 0 ? p.q_bias : kind == 1 ? p.k_bias : p.v_bias;
+  const size_t src = (size_t)t * p.in.row_stride + col;
+  const int pos = p.positions[t];
+  if (pos < 0) { if (lane == 0) set_error(p.err, kErrPosition, t, pos, 0); return; }
+
+  T* dst = nullptr;
+  T* dst_v = nullptr;
+  int zero_rows = 0;
+  if (kind == 0) {
+    dst = (T*)p.q_out + ((size_t)t * p.n_q_heads + head) * d;
+  } else {
+    const int r = p.tok_req[t];
+    if (r < 0 || r >= p.n_reqs) { if (lane == 0) set_error(p.err, kErrRequest, t, r, p.n_reqs); return; }
+    const int pidx = pos / p.page_size;
+    const int slot = pos - pidx * p.page_size;
+    const int page = (pidx < p.max_pages) ? p.block_table[(size_t)p.req_slot[r] * p.max_pages + pidx] : -1;
+    if (page < 0 || page >= p.num_pages) { if (lane == 0) set_error(p.err, kErrPage, t, pidx, page); return; }
+    const size_t row = ((size_t)page * p.n_kv_heads + head) * p.page_size + slot;
+    dst = (T*)(kind == 1 ? p.k_cache : p.v_cache) + row * d;
+    if (kind == 1 && p.v_off < 0) dst_v = (T*)p.v_cache + row * p.v_dim;
+    if (p.req_kv_len != nullptr) {
+      const int kv_len = p.req_kv_len[r], q_len = p.req_q_len[r];
+      if (pos == kv_len - 1 && pos - slot >= kv_len - q_len) zero_rows = p.page_size - 1 - slot;
+    }
+  }
+  const int chunks = d >> 2;
+  const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int z = 1; z <= zero_rows; ++z) {
+    for (int i = lane; i < chunks; i += 32) {
+      st4<T>(dst + (size_t)z * d + 4 * i, zero4);
+      if (dst_v != nullptr) st4<T>(dst_v + (size_t)z * d + 4 * i, zero4);
+    }
+  }
+
+  float* x = s_head[warp];
+  float4 own[4];
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = lane + 32 * k;
+    own[k] = zero4;
+    if (i >= chunks) continue;
+    float4 v = stacked_ld4<T>(p.in, src + 4 * i);
+    if (bias != nullptr) {
+      const float4 b = *reinterpret_cast<const float4*>(bias + head * d + 4 * i);
+      v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+    }
+    own[k] = v;
+    *reinterpret_cast<float4*>(x + 4 * i) = v;
+    ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+    if (kind == 2) st4<T>(dst + 4 * i, v);
+    if (dst_v != nullptr) st4<T>(dst_v + 4 * i, v);
+  }
+  if (kind == 2) return;
+  float factor = 1.0f;
+  if (p.head_norm) factor = rsqrtf(warp_sum(ss) / (float)d + p.eps);
+  if (kind == 0 && p.temp_every > 0) {
+    factor *= 1.0f + p.temp_coef * logf(floorf((float)(pos + 1) / (float)p.temp_every) + 1.0f);
+  }
+  const float* w = p.head_norm ? (kind == 0 ? p.q_norm : p.k_norm) : nullptr;
+  __syncwarp();
+  const int r = p.rope_table != nullptr ? p.rotary_dim : 0, half = r >> 1;
+  const float2* tab = p.rope_table + (size_t)t * half;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = lane + 32 * k;
+    if (i >= chunks) continue;
+    const float4 w4 = w != nullptr ? *reinterpret_cast<const float4*>(w + 4 * i) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    float v[4] = {own[k].x * factor * w4.x, own[k].y * factor * w4.y, own[k].z * factor * w4.z, own[k].w * factor * w4.w};
+    if (4 * i < r) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = 4 * i + j;
+        if (e < r) {
+          int partner, idx; bool first;
+          if (p.halves) { first = e < half; partner = first ? e + half : e - half; idx = first ? e : e - half; }
+          else { first = !(e & 1); partner = e ^ 1; idx = e >> 1; }
+          const float o = x[partner] * factor * (w != nullptr ? w[partner] : 1.0f);
+          const float2 cs = tab[idx];
+          v[j] = first ? v[j] * cs.x - o * cs.y : v[j] * cs.x + o * cs.y;
+        }
+      }
+    }
+    st4<T>(dst + 4 * i, make_float4(v[0], v[1], v[2], v[3]));
+  }
+}
+
 }  // namespace tk
 
 TK_API int tk_qkv_heads(const void* x, const float* parts, int n_parts, long long part_stride, int row_stride,
@@ -155,6 +262,12 @@ TK_API int tk_qkv_heads(const void* x, const float* parts, int n_parts, long lon
   const int heads_total = n_q_heads + n_kv_heads + (v_off >= 0 ? n_kv_heads : 0);
   const dim3 grid((unsigned)n_tokens, (unsigned)((heads_total + tk::kHeadsWarps - 1) / tk::kHeadsWarps));
   cudaError_t e = cudaSuccess;
+  const bool vec = k_dim % 4 == 0 && v_dim % 4 == 0 && row_stride % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 &&
+                   (v_off < 0 || v_off % 4 == 0);
+  if (vec) {
+    TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::qkv_heads_vec_kernel<T>, grid, dim3(tk::kHeadsWarps * 32), 0, stream, p));
+    return (int)e;
+  }
   TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::qkv_heads_kernel<T>, grid, dim3(tk::kHeadsWarps * 32), 0, stream, p));
   return (int)e;
 }

@@ -115,8 +115,10 @@ class MlpSpec:
 
 @FEED_FORWARDS.register("mlp")
 class Mlp:
-    """``W_down act(W_up x)`` without biases: a product, the activation (a kernel that also adds up the float32
-    partial sums of a split product, ``csrc/elementwise.cu``), a product."""
+    """``W_down act(W_up x)`` without biases.  In bfloat16 the activation rides in the epilogue of the first
+    product (steps of few tokens: the tcgen05 product whose cluster adds its splits up; many tokens: the product
+    on pairs of SMs), where the sizes allow; otherwise, and in float32, it is a kernel of its own that also adds
+    up the float32 partial sums of a split product (``csrc/elementwise.cu``)."""
 
     GRAPH_SAFE = True
 
@@ -140,7 +142,17 @@ class Mlp:
         err = step.err if step is not None else None
         if isinstance(h, OwedNorm):
             h = h.materialize()
-        act = ops.unary_act(linear(h, self.w_up, err=err), h.dtype, self.spec.activation)
+        n, name = h.shape[0], self.spec.activation
+        ff, width = self.spec.intermediate_size, self.spec.hidden_size
+        if h.dtype == torch.bfloat16 and err is not None and n <= SWAPPED_GEMM_MAX_TOKENS and ff % 128 == 0 and width % 8 == 0:
+            # few tokens: the cluster that adds the product's splits up applies the activation
+            splits, stages, cluster = ops.swapped_gemm_plan(ff, width, n)
+            act = ops.gemm_tc_swapped(self.w_up, h, err, splits, max_stages=stages, cluster=cluster, unary=name)
+        elif h.dtype == torch.bfloat16 and err is not None and ops.pair_gemm_takes(n, ff, width, fused=True):
+            # many tokens: the product on pairs of SMs applies it to its accumulators
+            act = ops.gemm_pair(h, self.w_up, err, unary=name)
+        else:
+            act = ops.unary_act(linear(h, self.w_up, err=err), h.dtype, name)
         return linear(act, self.w_down, err=err)
 
 
