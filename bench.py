@@ -1546,8 +1546,15 @@ def pukinex_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
         w_up, w_down = bf(ff, width) * width ** -0.5, bf(width, ff) * ff ** -0.5
         wgu, wd = bf(2 * ff_twin, width) * width ** -0.5, bf(width, ff_twin) * ff_twin ** -0.5
 
-        def mlp():
-            y = linear(ops.unary_act(linear(h, w_up, err=err), torch.bfloat16, "relu2"), w_down, err=err)
+        def mlp():         # as the part chooses
+            if n <= 64:
+                splits, stages, cluster = ops.swapped_gemm_plan(ff, width, n)
+                a = ops.gemm_tc_swapped(w_up, h, err, splits, max_stages=stages, cluster=cluster, unary="relu2")
+            elif ops.pair_gemm_takes(n, ff, width, fused=True):
+                a = ops.gemm_pair(h, w_up, err, unary="relu2")
+            else:
+                a = ops.unary_act(linear(h, w_up, err=err), torch.bfloat16, "relu2")
+            y = linear(a, w_down, err=err)
             ops.flush_chains()
             return y
 
@@ -1565,10 +1572,10 @@ def pukinex_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
             ops.flush_chains()
             return y
         if single:
-            row(f"feed-forward (up, relu squared, down), {name}", f"gated feed-forward of equal weights, {name}",
+            row(f"feed-forward (up with relu squared in its epilogue, down), {name}", f"gated feed-forward of equal weights, {name}",
                 _time_us(mlp, graph=True), _time_us(gated, graph=True), nbytes=2 * ff * width * 2, like_bytes=3 * ff_twin * width * 2)
         else:
-            row(f"feed-forward (up, relu squared, down), {name}", f"gated feed-forward of equal weights, {name}",
+            row(f"feed-forward (up with relu squared in its epilogue, down), {name}", f"gated feed-forward of equal weights, {name}",
                 _time_us(mlp), _time_us(gated), flops=4.0 * n * ff * width, like_flops=6.0 * n * ff_twin * width)
         up_sums = linear(h, w_up, err=err)
         gu_twin, act_twin = bf(n, 2 * ff_twin), torch.empty(n, ff_twin, dtype=torch.bfloat16, device=dev)

@@ -73,8 +73,8 @@ def test_ignored_keys_and_window():
 
 
 def test_registry_errors():
-    assert supported_architectures() == ["Ketalix", "Logivik", "Qwen3ForCausalLM", "Tarivik"]
-    with pytest.raises(ConfigError, match="Unsupported architecture 'LlamaForCausalLM'; supported: Ketalix, Logivik, Qwen3ForCausalLM, Tarivik"):
+    assert supported_architectures() == ["Ketalix", "Logivik", "Pukinex", "Qwen3ForCausalLM", "Tarivik"]
+    with pytest.raises(ConfigError, match="Unsupported architecture 'LlamaForCausalLM'; supported: Ketalix, Logivik, Pukinex, Qwen3ForCausalLM, Tarivik"):
         architecture_of({"architectures": ["LlamaForCausalLM"]})
     with pytest.raises(ConfigError, match="<missing>"):
         architecture_of({})

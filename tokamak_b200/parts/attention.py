@@ -543,15 +543,22 @@ class GatedAttention:
         return tensor_bytes(self.w_in, self.w_o, self.q_bias, self.k_bias, self.v_bias, self.q_norm, self.k_norm,
                             self.dist_bias)
 
-    def branch(self, h, step, cache_view, out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor:
+    TAKES_PROJ = True      # the stacked input projection may be part of a wider product (see ParallelMixer)
+
+    def branch(self, h, step, cache_view, out: torch.Tensor | None = None, out_scale: float = 1.0, proj=None,
+               proj_off: int = 0) -> torch.Tensor:
+        """The rows in front of the output projection, times ``out_scale``, into ``out`` or a new tensor.  ``proj``:
+        a product of ``h`` that holds this part's input projection in its columns from ``proj_off`` on."""
         spec = self.spec
         n = h.shape[0]
-        proj = linear(h, self.w_in, err=step.err)
+        if proj is None:
+            proj, proj_off = linear(h, self.w_in, err=step.err), 0
         q = torch.empty((n, spec.num_heads, spec.head_dim), dtype=h.dtype, device=h.device)
         table, rotary_dim = self.position.rotary_table(step)
         coef, every = spec.q_temp if spec.q_temp is not None else (0.0, 0)
-        ops.qkv_heads(proj, q, cache_view.k, cache_view.v, step, cache_view.table, q_off=self.q_off, k_off=self.k_off,
-                      v_off=self.v_off, q_bias=self.q_bias, k_bias=self.k_bias, v_bias=self.v_bias,
+        ops.qkv_heads(proj, q, cache_view.k, cache_view.v, step, cache_view.table, q_off=proj_off + self.q_off,
+                      k_off=proj_off + self.k_off, v_off=None if self.v_off is None else proj_off + self.v_off,
+                      q_bias=self.q_bias, k_bias=self.k_bias, v_bias=self.v_bias,
                       head_norm_eps=spec.head_norm_eps, q_norm=self.q_norm, k_norm=self.k_norm, table=table,
                       rotary_dim=rotary_dim, halves=self.halves, temp_coef=coef, temp_every=every)
         att = torch.empty((n, spec.num_heads, spec.v_head_dim), dtype=h.dtype, device=h.device)
@@ -566,7 +573,7 @@ class GatedAttention:
                 return res
             out.copy_(res)
             return out
-        return ops.gate_scale(att, proj, self.g_off, out=out, scale=out_scale,
+        return ops.gate_scale(att, proj, proj_off + self.g_off, out=out, scale=out_scale,
                               gate_group=spec.v_head_dim if spec.gate == "head" else 1)
 
     def forward(self, h, step, cache_view):

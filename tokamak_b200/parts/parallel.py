@@ -33,6 +33,10 @@ class ParallelMixer:
 
     is one product.  The factors are applied in float32 before the rows are rounded to the engine's dtype.
     The cache need is the dictionary of the halves' needs.
+
+    Halves that declare ``TAKES_PROJ = True`` keep their stacked input projection in ``w_in`` and take
+    ``branch(..., proj=, proj_off=)``: the two input projections are then stacked too and run as one product of
+    the shared input, each half reading its columns of the result from ``proj_off`` on.
     """
 
     def __init__(self, spec: ParallelMixerSpec, prefix: str, tensors: dict[str, torch.Tensor], rt: Runtime):
@@ -44,6 +48,11 @@ class ParallelMixer:
             if not (hasattr(half, "branch") and hasattr(half, "out_width") and hasattr(half, "w_o")):
                 raise ValueError(f"a {type(half).__name__} cannot be half of a parallel mixer: it has no branch()")
         self.w_o = torch.cat([self.left.w_o, self.right.w_o], dim=1).contiguous()
+        self.w_in = None
+        if all(getattr(half, "TAKES_PROJ", False) for half in (self.left, self.right)):
+            n_left = self.left.w_in.shape[0]
+            self.w_in = torch.cat([self.left.w_in, self.right.w_in], dim=0).contiguous()
+            self.left.w_in, self.right.w_in = self.w_in[:n_left], self.w_in[n_left:]      # one copy in memory
         self.prefill_heads = getattr(self.left, "prefill_heads", None) or getattr(self.right, "prefill_heads", None)
 
     @staticmethod
@@ -64,6 +73,12 @@ class ParallelMixer:
     def forward(self, h, step, cache_view):
         n, wl, wr = h.shape[0], self.left.out_width, self.right.out_width
         y = torch.empty((n, wl + wr), dtype=h.dtype, device=h.device)
-        self.left.branch(h, step, cache_view["left"], out=y[:, :wl], out_scale=self.spec.left_scale)
-        self.right.branch(h, step, cache_view["right"], out=y[:, wl:], out_scale=self.spec.right_scale)
+        if self.w_in is not None:
+            proj = linear(h, self.w_in, err=step.err)
+            self.left.branch(h, step, cache_view["left"], out=y[:, :wl], out_scale=self.spec.left_scale, proj=proj)
+            self.right.branch(h, step, cache_view["right"], out=y[:, wl:], out_scale=self.spec.right_scale, proj=proj,
+                              proj_off=self.left.w_in.shape[0])
+        else:
+            self.left.branch(h, step, cache_view["left"], out=y[:, :wl], out_scale=self.spec.left_scale)
+            self.right.branch(h, step, cache_view["right"], out=y[:, wl:], out_scale=self.spec.right_scale)
         return linear(y, self.w_o, err=step.err)

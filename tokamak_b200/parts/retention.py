@@ -96,16 +96,21 @@ class Retention:
     def weight_bytes(self) -> int:
         return tensor_bytes(self.w_in, self.w_o)
 
-    def branch(self, h, step, cache_view, out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor:
+    TAKES_PROJ = True      # the stacked input projection may be part of a wider product (see ParallelMixer)
+
+    def branch(self, h, step, cache_view, out: torch.Tensor | None = None, out_scale: float = 1.0, proj=None,
+               proj_off: int = 0) -> torch.Tensor:
+        """``proj``: a product of ``h`` that holds this part's input projection in its columns from ``proj_off`` on."""
         spec = self.spec
-        proj = linear(h, self.w_in, err=step.err)
+        if proj is None:
+            proj, proj_off = linear(h, self.w_in, err=step.err), 0
         table, rotary_dim = self.position.rotary_table(step)
-        prep = ops.retention_prepare(proj, self.decay, table, dtype=h.dtype, q_off=self.q_off, k_off=self.k_off,
-                                     v_off=self.v_off, heads=spec.num_heads, key_dim=spec.key_dim,
+        prep = ops.retention_prepare(proj, self.decay, table, dtype=h.dtype, q_off=proj_off + self.q_off,
+                                     k_off=proj_off + self.k_off, v_off=proj_off + self.v_off, heads=spec.num_heads, key_dim=spec.key_dim,
                                      value_dim=spec.value_dim, rotary_dim=rotary_dim, halves=self.halves,
                                      k_scale=self.k_scale)
         o = ops.gla_scan(prep, cache_view.records, step.req_q_start, step.req_q_len, step.req_slot, step.err)
-        return ops.gla_out(o, proj, self.g_off, None, spec.norm_eps, h.dtype, out=out, out_scale=out_scale)
+        return ops.gla_out(o, proj, proj_off + self.g_off, None, spec.norm_eps, h.dtype, out=out, out_scale=out_scale)
 
     def forward(self, h, step, cache_view):
         return linear(self.branch(h, step, cache_view), self.w_o, err=step.err)
