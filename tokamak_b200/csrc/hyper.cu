@@ -98,22 +98,23 @@ __global__ void hyper_mix_norm_kernel(HyperParams p) {
   }
 }
 
-constexpr int kHyperChunks = 4;     // pieces of four columns a thread keeps in registers
+constexpr int kHyperChunks = 4;     // most pieces of four columns a thread keeps in registers
 
 // The same for rows whose width is a multiple of 4 and at most 16 columns a thread: 16-byte accesses, the read
 // row stays in registers between the passes (sum, squared deviations, store), the norm's weight and bias are
 // asked for before the wait for the kernel in front.  The sums per column are formed in the same order as in
 // the kernel above, so both give the same stream.
-template <typename T>
+// K: pieces a thread holds; SMAX: the most copies the unrolled loops cover (both keep the registers to what is used).
+template <typename T, int K, int SMAX>
 __global__ void __launch_bounds__(512) hyper_mix_norm_vec_kernel(HyperParams p) {
   __shared__ float scratch[32];
   __shared__ float s_mix[kHyperMaxStreams * kHyperMaxStreams], s_write[kHyperMaxStreams], s_read[kHyperMaxStreams];
   pdl_trigger();
   const int S = p.n_streams;
   const int chunks = p.width >> 2;
-  float4 w4[kHyperChunks], b4[kHyperChunks];
+  float4 w4[K], b4[K];
 #pragma unroll
-  for (int k = 0; k < kHyperChunks; ++k) {
+  for (int k = 0; k < K; ++k) {
     const int i = threadIdx.x + k * blockDim.x;
     w4[k] = b4[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (i < chunks && p.norm_w != nullptr) {
@@ -137,26 +138,26 @@ __global__ void __launch_bounds__(512) hyper_mix_norm_vec_kernel(HyperParams p) 
   const bool store = pending && p.rows == nullptr;
   const size_t copy = (size_t)p.n_tokens * p.width;
   float* x = p.streams + (size_t)t * p.width;
-  float4 u[kHyperChunks];
+  float4 u[K];
   float sum = 0.0f;
 #pragma unroll
-  for (int k = 0; k < kHyperChunks; ++k) {
+  for (int k = 0; k < K; ++k) {
     const int i = threadIdx.x + k * blockDim.x;
     u[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (i >= chunks) continue;
-    float4 old[kHyperMaxStreams];
+    float4 old[SMAX];
 #pragma unroll
-    for (int s = 0; s < kHyperMaxStreams; ++s) {
+    for (int s = 0; s < SMAX; ++s) {
       if (s < S) old[s] = *reinterpret_cast<const float4*>(x + (size_t)s * copy + 4 * i);
     }
     if (pending) {
       const float4 y = stacked_ld4<T>(p.branch, (size_t)t * p.branch.row_stride + 4 * i);
 #pragma unroll
-      for (int to = 0; to < kHyperMaxStreams; ++to) {
+      for (int to = 0; to < SMAX; ++to) {
         if (to < S) {
           float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-          for (int s = 0; s < kHyperMaxStreams; ++s) {
+          for (int s = 0; s < SMAX; ++s) {
             if (s < S) {
               const float m = s_mix[s * S + to];
               v.x += m * old[s].x; v.y += m * old[s].y; v.z += m * old[s].z; v.w += m * old[s].w;
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(512) hyper_mix_norm_vec_kernel(HyperParams p) 
       }
     } else {
 #pragma unroll
-      for (int s = 0; s < kHyperMaxStreams; ++s) {
+      for (int s = 0; s < SMAX; ++s) {
         if (s < S) {
           const float rd = s_read[s];
           u[k].x += rd * old[s].x; u[k].y += rd * old[s].y; u[k].z += rd * old[s].z; u[k].w += rd * old[s].w;
@@ -184,7 +185,7 @@ __global__ void __launch_bounds__(512) hyper_mix_norm_vec_kernel(HyperParams p) 
   const float mean = block_sum(sum, scratch) / (float)p.width;
   float dev = 0.0f;
 #pragma unroll
-  for (int k = 0; k < kHyperChunks; ++k) {
+  for (int k = 0; k < K; ++k) {
     if ((int)(threadIdx.x + k * blockDim.x) < chunks) {
       u[k].x -= mean; u[k].y -= mean; u[k].z -= mean; u[k].w -= mean;
       dev += (u[k].x * u[k].x + u[k].y * u[k].y) + (u[k].z * u[k].z + u[k].w * u[k].w);
@@ -193,7 +194,7 @@ __global__ void __launch_bounds__(512) hyper_mix_norm_vec_kernel(HyperParams p) 
   const float rstd = rsqrtf(block_sum(dev, scratch) / (float)p.width + p.eps);
   T* out = (T*)p.out + (size_t)blockIdx.x * p.width;
 #pragma unroll
-  for (int k = 0; k < kHyperChunks; ++k) {
+  for (int k = 0; k < K; ++k) {
     const int i = threadIdx.x + k * blockDim.x;
     if (i < chunks) {
       st4<T>(out + 4 * i, make_float4(u[k].x * rstd * w4[k].x + b4[k].x, u[k].y * rstd * w4[k].y + b4[k].y,
@@ -241,9 +242,24 @@ TK_API int tk_hyper_mix_norm(float* streams, const void* y, const float* y_parts
     int threads = ((n_rows <= 296 ? chunks : (chunks + 1) / 2) + 31) / 32 * 32;
     if (threads > 512) threads = 512;
     if (threads < 64) threads = 64;
-    if (dtype == tk::kF32) e = tk::launch(tk::hyper_mix_norm_vec_kernel<float>, dim3((unsigned)n_rows), dim3(threads), 0, stream, p);
-    else if (dtype == tk::kBF16) e = tk::launch(tk::hyper_mix_norm_vec_kernel<__nv_bfloat16>, dim3((unsigned)n_rows), dim3(threads), 0, stream, p);
+    const int per_thread = (chunks + threads - 1) / threads;
+#define TK_HYPER_VEC(T, K, SMAX) \
+    e = tk::launch(tk::hyper_mix_norm_vec_kernel<T, K, SMAX>, dim3((unsigned)n_rows), dim3(threads), 0, stream, p)
+#define TK_HYPER_VEC_K(T, SMAX)                                    \
+    do {                                                           \
+      if (per_thread <= 1) { TK_HYPER_VEC(T, 1, SMAX); }           \
+      else if (per_thread <= 2) { TK_HYPER_VEC(T, 2, SMAX); }      \
+      else { TK_HYPER_VEC(T, 4, SMAX); }                           \
+    } while (0)
+#define TK_HYPER_VEC_S(T)                                          \
+    do {                                                           \
+      if (n_streams <= 2) { TK_HYPER_VEC_K(T, 2); } else { TK_HYPER_VEC_K(T, 8); }   \
+    } while (0)
+    if (dtype == tk::kF32) { TK_HYPER_VEC_S(float); } else if (dtype == tk::kBF16) { TK_HYPER_VEC_S(__nv_bfloat16); }
     else return (int)cudaErrorInvalidValue;
+#undef TK_HYPER_VEC_S
+#undef TK_HYPER_VEC_K
+#undef TK_HYPER_VEC
     return (int)e;
   }
   const size_t smem = (size_t)width * sizeof(float);
