@@ -1413,19 +1413,19 @@ def pukinex_config(s: dict) -> dict:
     copies of the residual stream.  Attention heads as the twin's; retention has the twin's recurrent state
     (width / 256 heads, 128 x 256)."""
     w, d = s["width"], s["dim"]
-    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5 * 8.0, "softcap": 30.0,
-           "rot": {"base": 5e5, "dims": d // 2, "scaling": {"factor": 8.0}}}
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5 * 8.0, "softcap": 40.0,
+           "rot": {"base": 1e4, "dims": d // 2, "scaling": {"factor": 4.0}}}
     left = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "bias_max": 2048,
-            "bias_buckets": 32, "q_temp": {"coef": 0.5, "every": 256}}
+            "bias_buckets": 32, "q_temp": {"coef": 0.3, "every": 512}}
     heads = w // 256
-    right = {"heads": heads, "dim": 128, "vdim": 256, "decay": [1.0 - 2.0 ** (-5 - (h % 6)) for h in range(heads)],
-             "rot": {"base": 1e6, "dims": 128}}
-    par = {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.5}
+    right = {"heads": heads, "dim": 128, "vdim": 256, "decay": [1.0 - 2.0 ** (-4 - (h % 5)) for h in range(heads)],
+             "rot": {"base": 1e5, "dims": 128}}
+    par = {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.4}
     mlp = {"kind": "dense", "ff": s["ff"] * 3 // 2}
     layers = [{"type": "parallel" if i % 2 == 0 else "attention", "mixer": par if i % 2 == 0 else att, "mlp": mlp}
               for i in range(s["layers"])]
     return {"architecture": "Pukinex", "vocab": s["vocab"], "width": w, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
-            "residual_mult": 0.7, "streams": 2, "logit_scale": 0.25, "logit_softcap": 30.0, "layers": layers}
+            "residual_mult": 0.8, "streams": 2, "logit_scale": 0.5, "logit_softcap": 25.0, "layers": layers}
 
 
 def pukinex_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> list[dict]:
@@ -1501,8 +1501,8 @@ def pukinex_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
         projl = bf(n, (2 * hq + 2 * hkv) * d)
         qb, kb, vb, qn, kn = f32(hq * d), f32(hkv * d), f32(hkv * d), f32(d), f32(d)
         left = lambda: ops.qkv_heads(projl, q, kc, vc, step, table, q_off=0, k_off=hq * d, v_off=(hq + hkv) * d, q_bias=qb,
-                                     k_bias=kb, v_bias=vb, head_norm_eps=1e-5, q_norm=qn, k_norm=kn, temp_coef=0.5, temp_every=256)
-        inv_half = (1.0 / (5e5 ** (torch.arange(0, d // 2, 2, dtype=torch.float32) / (d // 2))) / 8.0).to(dev)
+                                     k_bias=kb, v_bias=vb, head_norm_eps=1e-5, q_norm=qn, k_norm=kn, temp_coef=0.3, temp_every=512)
+        inv_half = (1.0 / (1e4 ** (torch.arange(0, d // 2, 2, dtype=torch.float32) / (d // 2))) / 4.0).to(dev)
         rot_half = ops.rope_table(step.positions, inv_half)
         proja = bf(n, (hq + hkv) * d + hq)
         attn = lambda: ops.qkv_heads(proja, q, kc, vc, step, table, q_off=0, k_off=hq * d, v_off=None, table=rot_half,
@@ -1525,7 +1525,7 @@ def pukinex_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
         att_rows = bf(n, hq * d)
         wide = torch.empty(n, hq * d + width, dtype=torch.bfloat16, device=dev)
         row(f"channel gate + branch factor into the stacked rows, {name}", None,
-            _time_us(lambda: ops.gate_scale(att_rows, projl, 0, out=wide[:, :hq * d], scale=0.6),
+            _time_us(lambda: ops.gate_scale(att_rows, projl, 0, out=wide[:, :hq * d], scale=0.7),
                      graph=single), 0.0, nbytes=3 * n * hq * d * 2)
         row(f"head gate, {name}", None,
             _time_us(lambda: ops.gate_scale(att_rows, proja, (hq + hkv) * d, gate_group=d), graph=single), 0.0,
@@ -1537,7 +1537,7 @@ def pukinex_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
         resid = f32(n, width)
         normed = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
         row(f"write to 2 copies + read + layer norm, {name}", f"output norm + layer scale + residual + input norm, {name}",
-            _time_us(lambda: ops.hyper_mix_norm(streams, branch, mix=mixm * 0.1, write=wr, read=rd, mult=0.7, norm_w=w1, norm_b=b1,
+            _time_us(lambda: ops.hyper_mix_norm(streams, branch, mix=mixm * 0.1, write=wr, read=rd, mult=0.8, norm_w=w1, norm_b=b1,
                                                 eps=1e-5, dtype=torch.bfloat16), graph=single),
             _time_us(lambda: ops.branch_norm_add(resid, branch, w1, w1, 1e-6, w1, normed, 1e-6), graph=single),
             nbytes=n * width * (2 + 16 + 2), like_bytes=n * width * (2 + 8 + 2))
@@ -1598,8 +1598,8 @@ def pukinex_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
         us_gout = _time_us(lambda: ops.gla_out(go, gproj, 2 * gh * gk + gh * gv, nw, 1e-6, torch.bfloat16), graph=single)
         gla_in = n * (2 * gh * gk + gh * gv + rk) * 2 + gp.numel() * 4
         rproj = bf(n, 2 * gh * gk + 2 * gh * gv) * 0.5
-        decay = torch.tensor([1.0 - 2.0 ** (-5 - (i % 6)) for i in range(gh)], device=dev)
-        inv_r = (1.0 / (1e6 ** (torch.arange(0, gk, 2, dtype=torch.float32) / gk))).to(dev)
+        decay = torch.tensor([1.0 - 2.0 ** (-4 - (i % 5)) for i in range(gh)], device=dev)
+        inv_r = (1.0 / (1e5 ** (torch.arange(0, gk, 2, dtype=torch.float32) / gk))).to(dev)
         rtab = ops.rope_table(step.positions, inv_r)
         rprep = lambda: ops.retention_prepare(rproj, decay, rtab, dtype=torch.bfloat16, q_off=0, k_off=gh * gk, v_off=2 * gh * gk,
                                               heads=gh, key_dim=gk, value_dim=gv, rotary_dim=gk, halves=True, k_scale=gk ** -0.5)
@@ -1617,12 +1617,12 @@ def pukinex_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
                      "note": "the same kernel: float32 on the CUDA cores, token by token"})
         row(f"retention unit norm + silu gate + branch factor into the stacked rows, {name}", f"gla output norm + gate, {name}",
             _time_us(lambda: ops.gla_out(ro, rproj, 2 * gh * gk + gh * gv, None, 1e-5, torch.bfloat16,
-                                         out=wide[:, hq * d:hq * d + gh * gv] if gh * gv <= width else None, out_scale=0.5),
+                                         out=wide[:, hq * d:hq * d + gh * gv] if gh * gv <= width else None, out_scale=0.4),
                      graph=single), us_gout, nbytes=n * gh * gv * (4 + 2 + 2))
         # ---- scaled and capped logits (float32, in place)
         if single:
             logits = f32(n, s["vocab"])
-            row(f"logit scale + cap, {name}", None, _time_us(lambda: ops.logits_scale_cap(logits, 0.25, 30.0), graph=True), 0.0,
+            row(f"logit scale + cap, {name}", None, _time_us(lambda: ops.logits_scale_cap(logits, 0.5, 25.0), graph=True), 0.0,
                 nbytes=2 * logits.numel() * 4)
     assert err.tolist()[0] == 0, err.tolist()
     return rows
