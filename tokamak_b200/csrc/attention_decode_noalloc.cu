@@ -19,7 +19,8 @@ extern "C" int tk_attention_decode(const void* q, void* out, const void* k_cache
                                    int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
                                    int head_dim, int page_size, int max_pages, int num_pages, int window,
                                    int n_splits, float scale, float softcap, const float* sinks,
-                                   int chunk, const float* slopes, cudaStream_t stream);
+                                   int chunk, const float* slopes, const float* dist_bias, int dist_len,
+                                   cudaStream_t stream);
 
 namespace {
 
@@ -94,5 +95,6 @@ TK_API int tk_attention_decode_noalloc(const void* q, void* out, const void* k_c
   if (rc != 0) return rc;
   return tk_attention_decode(q, out, k_cache, v_cache, scratch, counters, items, positions, tok_req, req_slot,
                              block_table, err, n_items, n_reqs, n_q_heads, n_kv_heads, head_dim,
-                             page_size, max_pages, num_pages, window, n_splits, scale, 0.0f, nullptr, 0, nullptr, stream);
+                             page_size, max_pages, num_pages, window, n_splits, scale, 0.0f, nullptr, 0, nullptr, nullptr, 0,
+                             stream);
 }
