@@ -1204,7 +1204,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                      slopes: torch.Tensor | None = None,
                      dist_bias: torch.Tensor | None = None) -> None:
     """Split-K paged attention for the single next tokens listed in ``items`` (bfloat16 only).
-    ``softcap``, ``sinks``, ``chunk`` and ``slopes`` as in :func:`attention_plain`."""
+    ``softcap``, ``sinks``, ``chunk``, ``slopes`` and ``dist_bias`` as in :func:`attention_plain`."""
     _want_sinks(sinks, q.shape[1])
     _want_sinks(slopes, q.shape[1])
     _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")

@@ -73,6 +73,16 @@ norms is: hand its tensors to :func:`linear` or to kernels of this library, or c
 never read ``xb`` or ``sumsq`` with other code.  A part that passes ``chain=`` to :func:`linear` itself
 holds to the same rule for what it gets back.
 
+**A residual stream in several copies.**  A model whose spec says ``streams > 1`` hands its blocks and its last
+norm a float32 tensor ``[streams, N, hidden]`` instead of ``[N, hidden]``.  A block over such a stream leaves a
+:class:`HyperBranch` pending (the sublayer's output with the weights of its write to every copy); a norm that
+knows it (``layernorm``) takes ``add_norm(resid, pending, rows, read=)`` and does the write, the weighted read and
+the norm in one kernel.
+
+``TAKES_PROJ = True`` (a mixer that can be half of a ``parallel`` mixer): its stacked input projection is ``w_in``
+and its ``branch`` takes ``proj=, proj_off=``, a product of the shared input that holds its columns from
+``proj_off`` on, so that both halves' input projections run as one product.
+
 Where a row says ``[N, hidden]`` a mixer or feed-forward may instead return what
 :func:`linear` gave it: a 3-D float32 tensor of partial sums ``[parts, N, hidden]``
 from a split-K product.  The norm that consumes it adds the parts up (a 32-bit sum);
